@@ -1,0 +1,128 @@
+/*
+ * nb200 -- C ABI of the B200 (sm_100a) kernel library behind the HTile translator.
+ *
+ * Every entry point takes raw device pointers, explicit extents, a dtype code and a CUDA stream
+ * (a cudaStream_t passed as void*).  Calls are asynchronous on that stream and never synchronise
+ * the device.  Nothing is allocated behind the caller's back: scratch memory is caller-provided
+ * and sized by the matching *_workspace_bytes function.  Every function that can fail returns an
+ * int: 0 on success, a negative NB200_ERR_* code otherwise, with a thread-local message available
+ * from nb200_last_error().  The library is safe to call from one host thread per GPU.
+ *
+ * Reference interfaces replaced (paths inside the reference project):
+ *   - the GPU kernel that src/neptune_mlir/translators/triton.py:63-77 emits for a func.func and
+ *     that tests/test_translators.py:184-194 launches as module.<sym_name>[grid](q, k, v, out):
+ *     tensors in memref-argument order, output written in place, launch on the current stream.
+ *   - tests/golden/flash_attention_triton.py:4-64 is the executable form of the attention program
+ *     (tests/data/flash_attention_htile.mlir:11-149) that nb200_attn_fwd implements.
+ */
+#ifndef NB200_H
+#define NB200_H
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NB200_OK 0
+#define NB200_ERR_BAD_ARG (-1)        /* null pointer, non-positive extent, misaligned pointer   */
+#define NB200_ERR_UNSUPPORTED (-2)    /* shape / dtype outside what the kernels implement        */
+#define NB200_ERR_LAUNCH (-3)         /* the CUDA runtime or driver rejected a call              */
+#define NB200_ERR_DEVICE_TIMEOUT (-4) /* a bounded device-side wait expired (see status word)    */
+
+/* dtype codes: element type of the storage tensors */
+#define NB200_F16 0
+#define NB200_BF16 1
+#define NB200_F32 2
+
+/* Number of 32-bit words in a status buffer (see nb200_attn_fwd). */
+#define NB200_STATUS_WORDS 4
+
+/* Library version as major*10000 + minor*100 + patch. */
+int nb200_version(void);
+
+/* Message of the last failing call on this host thread ("" if none). */
+const char *nb200_last_error(void);
+
+/*
+ * Fused attention forward: out = softmax(q k^T * scale) v, optionally causal.
+ * Replaces the kernel generated from tests/data/flash_attention_htile.mlir:11-149
+ * (golden: tests/golden/flash_attention_triton.py:4-64).
+ *
+ *   q, out : [B, H, Sq, D]   k, v : [B, H, Skv, D]   contiguous, element type `dtype`
+ *   scale_log2 : log2(e) * softmax scale (the program's constant at flash_attention_htile.mlir:24);
+ *                scores are taken to the exp2 domain exactly as the program does
+ *   causal     : query row i sees keys j <= i + (Skv - Sq)
+ *   status     : device buffer of NB200_STATUS_WORDS int32, zeroed by the caller, or NULL.  If a
+ *                bounded device-side wait expires the kernel records where in status[0..3] and
+ *                finishes without completing the output; read it with nb200_status_read.
+ *
+ * f16 / bf16 with D == 128 and Sq, Skv multiples of 128 run on tcgen05 tensor cores with TMA-staged
+ * tiles; f32 (and any other D <= 256, any Sq/Skv) runs on an exact-fp32 SIMT kernel.
+ */
+int nb200_attn_fwd(const void *q, const void *k, const void *v, void *out,
+                   int B, int H, int Sq, int Skv, int D, int dtype,
+                   float scale_log2, int causal, int *status, void *stream);
+
+/* Copies a status buffer to the host after synchronising `stream`; returns NB200_ERR_DEVICE_TIMEOUT
+ * if status[0] != 0, NB200_OK if it is clear. host_out may be NULL. */
+int nb200_status_read(const int *status, int *host_out, void *stream);
+
+/*
+ * Split-K flash-decoding with grouped-query attention (no counterpart kernel in the reference; the
+ * operator follows the reference's [B, H, S, D] layout convention, flash_attention_htile.mlir:12-15).
+ *
+ *   q : [B, Hq, D]      k, v : [B, Hkv, Lkv, D]      (f16 or bf16, D == 128, Hq % Hkv == 0)
+ *   partials : fp32 [B, Hq, n_splits, D + 2]; per (b, hq, split) the un-normalised output o[D]
+ *              followed by m (running maximum, exp2 domain) and l (sum of 2^(x - m))
+ *   scale_log2 : log2(e) * softmax scale
+ * Lkv must be a multiple of n_splits, and Lkv / n_splits a multiple of 16.
+ */
+size_t nb200_decode_workspace_bytes(int B, int Hq, int D, int n_splits);
+
+int nb200_decode_splitk(const void *q, const void *k, const void *v, float *partials,
+                        int B, int Hq, int Hkv, int Lkv, int D, int n_splits, int dtype,
+                        float scale_log2, void *stream);
+
+/*
+ * Log-sum-exp combine of partials.  Partial (row, split) starts at
+ * partials + row * row_stride + split * split_stride (strides in floats), so the same call merges
+ * the splits of one GPU (row_stride = n_splits*(D+2), split_stride = D+2) and the per-GPU partials
+ * gathered from several GPUs (row_stride = D+2, split_stride = rows*(D+2)).
+ *   out_dtype NB200_F16 / NB200_BF16 : out is [rows, D], normalised and rounded
+ *   out_dtype NB200_F32              : out is [rows, D + 2] fp32, again a partial (o, m, l),
+ *                                      ready to be merged once more
+ */
+int nb200_decode_combine(const float *partials, void *out, int rows, int D, int n_splits,
+                         long long row_stride, long long split_stride, int out_dtype, void *stream);
+
+/*
+ * Mamba-1 selective scan forward (no counterpart in the reference).
+ *   u, delta, z, out : [B, Dm, L] (L contiguous), f16 or bf16; delta already soft-plused
+ *   A : fp32 [Dm, N]   Bm, Cm : [B, N, L]   Dskip : fp32 [Dm]   N == 16
+ *   h <- exp(delta*A) h + delta*Bm*u ;  y = sum_n Cm h + Dskip u ;  out = y * silu(z)
+ * L must be a multiple of 64 and Dm a multiple of 32.
+ */
+int nb200_selective_scan_fwd(const void *u, const void *delta, const float *A, const void *Bm,
+                             const void *Cm, const float *Dskip, const void *z, void *out,
+                             int B, int Dm, int L, int N, int dtype, void *stream);
+
+/*
+ * Mamba-2 SSD chunked scan forward (no counterpart in the reference).
+ *   x, y : [B, L, H, P]   dt : fp32 [B, L, H] (already soft-plused)   A : fp32 [H]
+ *   Bm, Cm : [B, L, G, N]  (head h reads group h / (H / G))
+ *   workspace : nb200_ssd_workspace_bytes(...) bytes of device memory (chunk states and decays)
+ * P == 64, N == 128, chunk in {64, 128, 256}, L a multiple of chunk.
+ */
+size_t nb200_ssd_workspace_bytes(int B, int L, int H, int P, int N, int G, int chunk);
+
+int nb200_ssd_chunk_scan_fwd(const void *x, const float *dt, const float *A, const void *Bm,
+                             const void *Cm, void *y, void *workspace,
+                             int B, int L, int H, int P, int N, int G, int chunk, int dtype,
+                             void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* NB200_H */

@@ -1,0 +1,388 @@
+// Fused attention forward on Blackwell tensor cores (f16 / bf16 storage, D = 128).
+//
+// One CTA computes a tile of 128 query rows of one (batch, head) against the KV sequence in blocks
+// of 128 rows, with the online softmax of the HTile program
+// (tests/data/flash_attention_htile.mlir:40-143 of the reference) kept in the exp2 domain:
+//
+//   warp 4 (one lane)   TMA producer: Q once, then K(j), V(j) into single 32 KB buffers each,
+//                       128-byte swizzled, re-armed as soon as the MMA that read them has retired
+//   warp 5 (one lane)   MMA issuer: S = Q K(j)^T (8 x tcgen05.mma 128x128x16, operands in smem,
+//                       accumulator in TMEM columns 0..127), then O += P V(j) with P read from
+//                       TMEM (it overwrites S in place as packed 16-bit) and V as an MN-major
+//                       smem operand, accumulator in TMEM columns 128..255
+//   warps 0-3           softmax: thread r owns row r (TMEM lane r), so row max and row sum need
+//                       no cross-thread traffic; two passes over S (max, then exp2 / sum / pack);
+//                       O is rescaled in TMEM only when a row maximum grows by more than 2^8,
+//                       which leaves the result unchanged (the same stale maximum scales P and
+//                       the running sum) but makes the rescale rare
+//
+// Two CTAs are resident per SM (98 KB smem, 256 TMEM columns each), so one CTA's softmax overlaps
+// the other's MMAs.  Tiles are numbered so that CTAs running at the same time work on the same few
+// heads (K/V stay in L2) and, for causal problems, the long tiles of a head are issued first.
+// Every wait is bounded; on expiry the CTA records a code in the status words and unwinds.
+#include <cuda.h>
+
+#include "nb200_common.cuh"
+#include "sm100_primitives.cuh"
+
+namespace nb200 {
+namespace {
+
+using namespace sm100;
+
+constexpr int kBM = 128;            // query rows per CTA
+constexpr int kBN = 128;            // kv rows per step
+constexpr int kD = 128;             // head dimension
+constexpr int kThreads = 192;
+constexpr int kTileBytes = kBM * kD * 2;        // 32 KB: two 64-column boxes of 16 KB
+constexpr int kBoxBytes = kTileBytes / 2;
+constexpr int kTmemCols = 256;
+constexpr int kSmemBytes = 3 * kTileBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr float kRescaleThreshold = 8.0f;       // log2 units
+
+enum : int { kErrProducer = 1, kErrMma = 2, kErrSoftmax = 3, kErrEpilogue = 4 };
+
+struct Barriers {
+  uint64_t q_full, k_full, k_empty, v_full, v_empty, s_full, p_full, o_full;
+  uint32_t tmem_base;
+  int abort_flag;
+  int skip;
+};
+
+__device__ __forceinline__ void report(int *status, int code, int detail) {
+  if (status && atomicCAS(status, 0, code) == 0) {
+    status[1] = static_cast<int>(blockIdx.x);
+    status[2] = detail;
+    status[3] = static_cast<int>(threadIdx.x);
+  }
+}
+
+template <int DT>
+__global__ void __launch_bounds__(kThreads, 2)
+attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                        const __grid_constant__ CUtensorMap tm_v, uint16_t *__restrict__ out, int Sq, int Skv,
+                        int n_qtiles, float scale_log2, int causal, int *status) {
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  unsigned char *smem = smem_raw + (base - raw);
+  const uint32_t sQ = base, sK = base + kTileBytes, sV = base + 2 * kTileBytes;
+  Barriers *bars = reinterpret_cast<Barriers *>(smem + 3 * kTileBytes);
+  volatile int *abort_flag = &bars->abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // tile -> (head, query tile): consecutive CTAs share a head; causal tiles longest first
+  const int bh = blockIdx.x / n_qtiles;
+  const int qi = blockIdx.x % n_qtiles;
+  const int qt = causal ? (n_qtiles - 1 - qi) : qi;
+  const int kv_off = Skv - Sq;                                   // causal diagonal offset (multiple of 128)
+  const int nblk = causal ? (qt + kv_off / kBN + 1) : (Skv / kBN);
+  const int q_row0 = bh * Sq + qt * kBM;                          // row in the [B*H*Sq, D] view
+  const int kv_row0 = bh * Skv;
+
+  if (threadIdx.x == 0) {
+    bars->abort_flag = 0;
+    bars->skip = (status != nullptr && *reinterpret_cast<volatile int *>(status) != 0) ? 1 : 0;
+    mbar_init(smem_u32(&bars->q_full), 1);
+    mbar_init(smem_u32(&bars->k_full), 1);
+    mbar_init(smem_u32(&bars->k_empty), 1);
+    mbar_init(smem_u32(&bars->v_full), 1);
+    mbar_init(smem_u32(&bars->v_empty), 1);
+    mbar_init(smem_u32(&bars->s_full), 1);
+    mbar_init(smem_u32(&bars->p_full), 128);
+    mbar_init(smem_u32(&bars->o_full), 1);
+    fence_barrier_init();
+    fence_proxy_async_smem();
+  }
+  __syncthreads();
+  if (bars->skip) return;  // an earlier CTA of this launch already reported a failure
+
+  if (warp == 5) {
+    tmem_alloc(smem_u32(&bars->tmem_base), kTmemCols);
+    tmem_relinquish();
+  }
+  if (warp == 4 && lane == 0) {
+    tma_prefetch_desc(&tm_q);
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars->tmem_base;
+  const uint32_t tS = tmem, tO = tmem + kBN;
+
+  const uint32_t b_q_full = smem_u32(&bars->q_full), b_k_full = smem_u32(&bars->k_full),
+                 b_k_empty = smem_u32(&bars->k_empty), b_v_full = smem_u32(&bars->v_full),
+                 b_v_empty = smem_u32(&bars->v_empty), b_s_full = smem_u32(&bars->s_full),
+                 b_p_full = smem_u32(&bars->p_full), b_o_full = smem_u32(&bars->o_full);
+
+  if (warp == 4) {
+    // ================================ TMA producer ================================
+    if (lane == 0) {
+      mbar_arrive_expect_tx(b_q_full, kTileBytes);
+      tma_load_2d(sQ, &tm_q, 0, q_row0, b_q_full);
+      tma_load_2d(sQ + kBoxBytes, &tm_q, 64, q_row0, b_q_full);
+      int issued_k = 0, issued_v = 0;
+      bool ok = true;
+      for (int j = 0; j < nblk && ok; ++j) {
+        const uint32_t ph = j & 1;
+        ok = mbar_wait(b_k_empty, ph ^ 1, abort_flag);
+        if (!ok) { report(status, kErrProducer, 2 * j); break; }
+        mbar_arrive_expect_tx(b_k_full, kTileBytes);
+        tma_load_2d(sK, &tm_k, 0, kv_row0 + j * kBN, b_k_full);
+        tma_load_2d(sK + kBoxBytes, &tm_k, 64, kv_row0 + j * kBN, b_k_full);
+        ++issued_k;
+        ok = mbar_wait(b_v_empty, ph ^ 1, abort_flag);
+        if (!ok) { report(status, kErrProducer, 2 * j + 1); break; }
+        mbar_arrive_expect_tx(b_v_full, kTileBytes);
+        tma_load_2d(sV, &tm_v, 0, kv_row0 + j * kBN, b_v_full);
+        tma_load_2d(sV + kBoxBytes, &tm_v, 64, kv_row0 + j * kBN, b_v_full);
+        ++issued_v;
+      }
+      if (!ok) {
+        // Unwinding: let the copies already in flight land before the CTA's shared memory goes away.
+        mbar_wait(b_q_full, 0, abort_flag);
+        for (int spin = 0; spin < 100000; ++spin) {
+          const bool kd = issued_k == 0 || mbar_try_wait(b_k_full, (issued_k - 1) & 1);
+          const bool vd = issued_v == 0 || mbar_try_wait(b_v_full, (issued_v - 1) & 1);
+          if (kd && vd) break;
+          __nanosleep(100);
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 5) {
+    // ================================ MMA issuer ==================================
+    if (lane == 0) {
+      constexpr int fmt = (DT == NB200_BF16) ? 1 : 0;
+      constexpr uint32_t idesc_qk = umma_idesc_f16(fmt, 0, kBM, kBN);
+      constexpr uint32_t idesc_pv = umma_idesc_f16(fmt, 1, kBM, kD);
+      bool ok = mbar_wait(b_q_full, 0, abort_flag);
+      if (!ok) report(status, kErrMma, -1);
+      for (int j = 0; j < nblk && ok; ++j) {
+        const uint32_t ph = j & 1;
+        ok = mbar_wait(b_k_full, ph, abort_flag);
+        if (!ok) { report(status, kErrMma, 3 * j); break; }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < kD / 16; ++kk) {
+          // 16 elements of K per MMA = 32 bytes inside the 128-byte swizzled row
+          const uint32_t off = (kk >> 2) * kBoxBytes + (kk & 3) * 32;
+          umma_ss(tS, umma_desc_sw128(sQ + off, 16, 1024), umma_desc_sw128(sK + off, 16, 1024), idesc_qk,
+                  kk > 0);
+        }
+        umma_commit(b_k_empty);
+        umma_commit(b_s_full);
+
+        ok = mbar_wait(b_p_full, ph, abort_flag);
+        if (!ok) { report(status, kErrMma, 3 * j + 1); break; }
+        ok = mbar_wait(b_v_full, ph, abort_flag);
+        if (!ok) { report(status, kErrMma, 3 * j + 2); break; }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < kBN / 16; ++kk) {
+          // P: 16 packed 16-bit values = 8 TMEM columns; V: 16 kv rows = 2 KB, column blocks 16 KB apart
+          umma_ts(tO, tS + kk * 8, umma_desc_sw128(sV + kk * 2048, kBoxBytes, 1024), idesc_pv,
+                  (j > 0 || kk > 0) ? 1u : 0u);
+        }
+        umma_commit(b_v_empty);
+      }
+      if (ok) umma_commit(b_o_full);
+    }
+    __syncwarp();
+  } else {
+    // ================================ softmax + epilogue ==========================
+    const int r = warp * 32 + lane;                         // row in the tile == TMEM lane
+    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    const int jdiag = causal ? (nblk - 1) : -1;
+    float m_used = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < nblk; ++j) {
+      // warp-uniform outcome: the TMEM accesses below are warp-collective
+      ok = __all_sync(0xffffffffu, mbar_wait(b_s_full, j & 1, abort_flag));
+      if (!ok) { report(status, kErrSoftmax, j); break; }
+      tc_fence_after();
+      const bool diag = (j == jdiag);
+
+      // ---- pass 1: row maximum of this block ----
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < kBN / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld32(tS + lane_addr + c * 32, v);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float s = __uint_as_float(v[i]);
+          mx = (diag && (c * 32 + i > r)) ? mx : fmaxf(mx, s);
+        }
+      }
+      const float m_blk = mx * scale_log2;                   // scale_log2 > 0
+      if (j == 0) {
+        m_used = m_blk;
+      } else {
+        const bool need = m_blk > m_used + kRescaleThreshold;
+        if (__any_sync(0xffffffffu, need)) {
+          const float f = need ? ex2(m_used - m_blk) : 1.f;
+          if (need) m_used = m_blk;
+          l *= f;
+          // PV(j-1) has retired: the commit that signalled s_full(j) was issued after it.
+#pragma unroll 1
+          for (int c = 0; c < kD / 32; ++c) {
+            uint32_t v[32];
+            tmem_ld32(tO + lane_addr + c * 32, v);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
+            tmem_st32(tO + lane_addr + c * 32, v);
+          }
+          tmem_wait_st();
+        }
+      }
+
+      // ---- pass 2: p = 2^(s*scale - m), row sum, pack to 16 bit, write P over S ----
+      const float neg_m = -m_used;
+#pragma unroll 1
+      for (int c = 0; c < kBN / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld32(tS + lane_addr + c * 32, v);
+        tmem_wait_ld();
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float p0 = ex2(fmaf(__uint_as_float(v[2 * i]), scale_log2, neg_m));
+          float p1 = ex2(fmaf(__uint_as_float(v[2 * i + 1]), scale_log2, neg_m));
+          if (diag) {
+            p0 = (c * 32 + 2 * i > r) ? 0.f : p0;
+            p1 = (c * 32 + 2 * i + 1 > r) ? 0.f : p1;
+          }
+          l += p0 + p1;
+          pk[i] = pack2<DT>(p0, p1);
+        }
+        tmem_st16(tS + lane_addr + c * 16, pk);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(b_p_full);
+    }
+
+    // ---- epilogue: O / l -> storage dtype -> global ----
+    if (ok) {
+      ok = __all_sync(0xffffffffu, mbar_wait(b_o_full, 0, abort_flag));
+      if (!ok) report(status, kErrEpilogue, 0);
+    }
+    if (ok) {
+      tc_fence_after();
+      const float inv = 1.f / l;
+      uint16_t *dst = out + (static_cast<size_t>(q_row0) + r) * kD;
+#pragma unroll 1
+      for (int c = 0; c < kD / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld32(tO + lane_addr + c * 32, v);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          uint4 w;
+          w.x = pack2<DT>(__uint_as_float(v[8 * i + 0]) * inv, __uint_as_float(v[8 * i + 1]) * inv);
+          w.y = pack2<DT>(__uint_as_float(v[8 * i + 2]) * inv, __uint_as_float(v[8 * i + 3]) * inv);
+          w.z = pack2<DT>(__uint_as_float(v[8 * i + 4]) * inv, __uint_as_float(v[8 * i + 5]) * inv);
+          w.w = pack2<DT>(__uint_as_float(v[8 * i + 6]) * inv, __uint_as_float(v[8 * i + 7]) * inv);
+          *reinterpret_cast<uint4 *>(dst + c * 32 + i * 8) = w;
+        }
+      }
+    }
+  }
+
+  // ================================ tear-down =====================================
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem, kTmemCols);
+  }
+}
+
+// cuTensorMapEncodeTiled, resolved through the runtime so that the library does not link libcuda.
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
+                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                   CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+// [rows, 128] 16-bit row-major tensor, boxes of 128 rows x 64 columns, 128-byte swizzle.
+int make_tile_map(CUtensorMap *tm, const void *ptr, long long rows, int dtype) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  NB200_REQUIRE(enc, NB200_ERR_LAUNCH, "attn_fwd: cuTensorMapEncodeTiled is not available from the driver");
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(kD), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(kD) * 2};
+  const cuuint32_t box[2] = {64, static_cast<cuuint32_t>(kBM)};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = enc(tm, dtype == NB200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                         2, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  NB200_REQUIRE(r == CUDA_SUCCESS, NB200_ERR_LAUNCH, "attn_fwd: cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return NB200_OK;
+}
+
+template <int DT>
+int launch_tc(const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv, void *out, int BH, int Sq,
+              int Skv, float scale_log2, int causal, int *status, cudaStream_t st) {
+  // per-device attribute: set on every call so that any current device is covered
+  NB200_CHECK_CUDA(cudaFuncSetAttribute(attn_fwd_tcgen05_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        kSmemBytes));
+  const int n_qtiles = Sq / kBM;
+  attn_fwd_tcgen05_kernel<DT><<<dim3(BH * n_qtiles), dim3(kThreads), kSmemBytes, st>>>(
+      tq, tk, tv, static_cast<uint16_t *>(out), Sq, Skv, n_qtiles, scale_log2, causal, status);
+  NB200_CHECK_CUDA(cudaGetLastError());
+  return NB200_OK;
+}
+
+}  // namespace
+
+int attn_simt_launch(const void *q, const void *k, const void *v, void *out, int B, int H, int Sq, int Skv,
+                     int D, int dtype, float scale_log2, int causal, cudaStream_t st);
+
+}  // namespace nb200
+
+using namespace nb200;
+
+extern "C" int nb200_attn_fwd(const void *q, const void *k, const void *v, void *out, int B, int H, int Sq,
+                              int Skv, int D, int dtype, float scale_log2, int causal, int *status,
+                              void *stream) {
+  NB200_REQUIRE(q && k && v && out, NB200_ERR_BAD_ARG, "attn_fwd: null pointer");
+  NB200_REQUIRE(B > 0 && H > 0 && Sq > 0 && Skv > 0 && D > 0, NB200_ERR_BAD_ARG, "attn_fwd: non-positive extent");
+  NB200_REQUIRE(scale_log2 > 0.f, NB200_ERR_BAD_ARG, "attn_fwd: scale_log2 must be positive");
+  NB200_REQUIRE(!causal || Skv >= Sq, NB200_ERR_UNSUPPORTED, "attn_fwd: causal needs Skv >= Sq");
+  NB200_REQUIRE(dtype == NB200_F16 || dtype == NB200_BF16 || dtype == NB200_F32, NB200_ERR_UNSUPPORTED,
+                "attn_fwd: dtype %d", dtype);
+  auto st = static_cast<cudaStream_t>(stream);
+  const bool tensor_path = (dtype == NB200_F16 || dtype == NB200_BF16) && D == kD && Sq % kBM == 0 &&
+                           Skv % kBN == 0 && (long long)B * H * (Sq / kBM) < (1ll << 31) &&
+                           (long long)B * H * (long long)(Sq > Skv ? Sq : Skv) < (1ll << 31);
+  if (!tensor_path) return attn_simt_launch(q, k, v, out, B, H, Sq, Skv, D, dtype, scale_log2, causal, st);
+
+  NB200_REQUIRE(aligned16(q) && aligned16(k) && aligned16(v) && aligned16(out), NB200_ERR_BAD_ARG,
+                "attn_fwd: tensors must be 16-byte aligned");
+  CUtensorMap tq, tk, tv;
+  int rc;
+  if ((rc = make_tile_map(&tq, q, (long long)B * H * Sq, dtype)) != NB200_OK) return rc;
+  if ((rc = make_tile_map(&tk, k, (long long)B * H * Skv, dtype)) != NB200_OK) return rc;
+  if ((rc = make_tile_map(&tv, v, (long long)B * H * Skv, dtype)) != NB200_OK) return rc;
+  if (dtype == NB200_BF16)
+    return launch_tc<NB200_BF16>(tq, tk, tv, out, B * H, Sq, Skv, scale_log2, causal, status, st);
+  return launch_tc<NB200_F16>(tq, tk, tv, out, B * H, Sq, Skv, scale_log2, causal, status, st);
+}

@@ -1,0 +1,373 @@
+// Split-K flash-decoding with grouped-query attention, and the log-sum-exp combine.
+//
+// The path is HBM-bound (about 4 FLOP per byte of KV cache), so the kernel is built around
+// streaming K and V exactly once with 128-bit coalesced loads:
+//   * one CTA per (split, kv head, sequence); the G query heads that share a kv head are all
+//     evaluated by the same CTA, so each K/V row is read once and used G times;
+//   * a K/V row of 128 elements is 16 lanes x 16 bytes; a warp therefore reads two rows per load
+//     instruction and keeps 4 K and 4 V loads in flight (8 rows per warp iteration);
+//   * the 16-lane dot-product reduction is a butterfly that leaves head g's score on lanes whose
+//     bits 3:2 equal g (5 shuffles for G = 4 instead of 16), the online softmax runs on those lanes,
+//     and the probabilities are broadcast back for the PV accumulation;
+//   * all arithmetic is fp32 (packed f32x2 FMAs), scores in the exp2 domain.
+// Per (row, split) the kernel writes the un-normalised output, the running maximum and the sum,
+// which nb200_decode_combine merges.
+#include "nb200_common.cuh"
+
+namespace nb200 {
+namespace {
+
+constexpr int kDecodeThreads = 256;
+constexpr int kDecodeWarps = kDecodeThreads / 32;
+constexpr int kHeadDim = 128;
+constexpr int kPairs = 4;                               // row pairs per warp iteration
+constexpr int kRowsPerIter = kDecodeWarps * kPairs * 2;  // 64 rows per CTA iteration
+
+__device__ __forceinline__ uint4 ldg_stream(const void *p) {
+  uint4 r;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+               : "l"(p));
+  return r;
+}
+
+template <int DT, int G>
+__global__ void __launch_bounds__(kDecodeThreads, (G >= 8 ? 1 : 2))
+decode_splitk_kernel(const uint16_t *__restrict__ q, const uint16_t *__restrict__ k,
+                     const uint16_t *__restrict__ v, float *__restrict__ partials, int Hkv, int Lkv,
+                     int n_splits, float scale_log2) {
+  const int split = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
+  const int Hq = Hkv * G;
+  const int T = Lkv / n_splits;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int half = lane >> 4, c = lane & 15;
+
+  // q for the G heads of this kv head, this lane's 8 elements, pre-multiplied by the scale.
+  uint64_t q2[G][4];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    const uint4 w = *reinterpret_cast<const uint4 *>(q + ((size_t)b * Hq + hkv * G + g) * kHeadDim + c * 8);
+    const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      const float2 f = unpack2<DT>(ws[p]);
+      q2[g][p] = f2_pack(f.x * scale_log2, f.y * scale_log2);
+    }
+  }
+
+  const size_t kv_base = (((size_t)b * Hkv + hkv) * Lkv + (size_t)split * T) * kHeadDim + c * 8;
+  const uint16_t *kp = k + kv_base;
+  const uint16_t *vp = v + kv_base;
+
+  uint64_t o2[G][4];
+#pragma unroll
+  for (int g = 0; g < G; ++g)
+#pragma unroll
+    for (int p = 0; p < 4; ++p) o2[g][p] = 0ull;
+  // Running max / sum of the head this lane owns after the butterfly (head index = lane bits 3:2
+  // for G = 4; for other G every lane tracks all heads through the generic path below).
+  float m_run[G == 4 ? 1 : G], l_run[G == 4 ? 1 : G];
+#pragma unroll
+  for (int g = 0; g < (G == 4 ? 1 : G); ++g) {
+    m_run[g] = -INFINITY;
+    l_run[g] = 0.f;
+  }
+
+  for (int r0 = warp * (kPairs * 2); r0 < T; r0 += kRowsPerIter) {
+    uint4 kr[kPairs], vr[kPairs];
+    bool valid[kPairs];
+#pragma unroll
+    for (int i = 0; i < kPairs; ++i) {
+      const int r = r0 + 2 * i + half;
+      valid[i] = r < T;
+      if (valid[i]) {
+        kr[i] = ldg_stream(kp + (size_t)r * kHeadDim);
+        vr[i] = ldg_stream(vp + (size_t)r * kHeadDim);
+      } else {
+        kr[i] = make_uint4(0, 0, 0, 0);
+        vr[i] = make_uint4(0, 0, 0, 0);
+      }
+    }
+
+    // ---- scores: partial dot products over this lane's 8 elements ----
+    float part[kPairs][G];
+#pragma unroll
+    for (int i = 0; i < kPairs; ++i) {
+      const uint32_t ws[4] = {kr[i].x, kr[i].y, kr[i].z, kr[i].w};
+      uint64_t k2[4];
+#pragma unroll
+      for (int p = 0; p < 4; ++p) {
+        const float2 f = unpack2<DT>(ws[p]);
+        k2[p] = f2_pack(f.x, f.y);
+      }
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        uint64_t acc = f2_mul(q2[g][0], k2[0]);
+#pragma unroll
+        for (int p = 1; p < 4; ++p) acc = f2_fma(q2[g][p], k2[p], acc);
+        const float2 a = f2_unpack(acc);
+        part[i][g] = a.x + a.y;
+      }
+    }
+
+    float pg[kPairs][G];  // probabilities of every head for this lane's rows
+    float alpha[G];
+    if constexpr (G == 4) {
+      // Butterfly over the 16 lanes of a row: afterwards lanes with bits 3:2 == g hold head g.
+      const bool b3 = lane & 8, b2 = lane & 4;
+      float s[kPairs];
+#pragma unroll
+      for (int i = 0; i < kPairs; ++i) {
+        float a0 = b3 ? part[i][2] : part[i][0];
+        float a1 = b3 ? part[i][3] : part[i][1];
+        const float s0 = b3 ? part[i][0] : part[i][2];
+        const float s1 = b3 ? part[i][1] : part[i][3];
+        a0 += __shfl_xor_sync(0xffffffffu, s0, 8);
+        a1 += __shfl_xor_sync(0xffffffffu, s1, 8);
+        float x = b2 ? a1 : a0;
+        const float sx = b2 ? a0 : a1;
+        x += __shfl_xor_sync(0xffffffffu, sx, 4);
+        x += __shfl_xor_sync(0xffffffffu, x, 2);
+        x += __shfl_xor_sync(0xffffffffu, x, 1);
+        s[i] = valid[i] ? x : -INFINITY;
+      }
+      float mb = fmaxf(fmaxf(s[0], s[1]), fmaxf(s[2], s[3]));
+      mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, 16));
+      const float m_new = fmaxf(m_run[0], mb);
+      const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
+      const float a = ex2(m_run[0] - m_safe);
+      float p[kPairs], psum = 0.f;
+#pragma unroll
+      for (int i = 0; i < kPairs; ++i) {
+        p[i] = ex2(s[i] - m_safe);
+        psum += p[i];
+      }
+      l_run[0] = l_run[0] * a + psum;
+      m_run[0] = m_new;
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        alpha[g] = __shfl_sync(0xffffffffu, a, g << 2);
+#pragma unroll
+        for (int i = 0; i < kPairs; ++i) pg[i][g] = __shfl_sync(0xffffffffu, p[i], (lane & 16) | (g << 2));
+      }
+    } else {
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        float s[kPairs];
+#pragma unroll
+        for (int i = 0; i < kPairs; ++i) {
+          float x = part[i][g];
+          x += __shfl_xor_sync(0xffffffffu, x, 8);
+          x += __shfl_xor_sync(0xffffffffu, x, 4);
+          x += __shfl_xor_sync(0xffffffffu, x, 2);
+          x += __shfl_xor_sync(0xffffffffu, x, 1);
+          s[i] = valid[i] ? x : -INFINITY;
+        }
+        float mb = fmaxf(fmaxf(s[0], s[1]), fmaxf(s[2], s[3]));
+        mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, 16));
+        const float m_new = fmaxf(m_run[g], mb);
+        const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
+        alpha[g] = ex2(m_run[g] - m_safe);
+        float psum = 0.f;
+#pragma unroll
+        for (int i = 0; i < kPairs; ++i) {
+          pg[i][g] = ex2(s[i] - m_safe);
+          psum += pg[i][g];
+        }
+        l_run[g] = l_run[g] * alpha[g] + psum;
+        m_run[g] = m_new;
+      }
+    }
+
+    // ---- o = o * alpha + sum_i p_i v_i ----
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      const uint64_t a2 = f2_pack(alpha[g], alpha[g]);
+#pragma unroll
+      for (int p = 0; p < 4; ++p) o2[g][p] = f2_mul(o2[g][p], a2);
+    }
+#pragma unroll
+    for (int i = 0; i < kPairs; ++i) {
+      const uint32_t ws[4] = {vr[i].x, vr[i].y, vr[i].z, vr[i].w};
+      uint64_t v2[4];
+#pragma unroll
+      for (int p = 0; p < 4; ++p) {
+        const float2 f = unpack2<DT>(ws[p]);
+        v2[p] = f2_pack(f.x, f.y);
+      }
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        const uint64_t p2 = f2_pack(pg[i][g], pg[i][g]);
+#pragma unroll
+        for (int p = 0; p < 4; ++p) o2[g][p] = f2_fma(p2, v2[p], o2[g][p]);
+      }
+    }
+  }
+
+  // ---- merge the two row halves of the warp, then the warps of the CTA ----
+  __shared__ float sm_o[kDecodeWarps][G][kHeadDim];
+  __shared__ float sm_m[kDecodeWarps][G], sm_l[kDecodeWarps][G];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      float2 f = f2_unpack(o2[g][p]);
+      f.x += __shfl_xor_sync(0xffffffffu, f.x, 16);
+      f.y += __shfl_xor_sync(0xffffffffu, f.y, 16);
+      if (half == 0) {
+        sm_o[warp][g][c * 8 + 2 * p] = f.x;
+        sm_o[warp][g][c * 8 + 2 * p + 1] = f.y;
+      }
+    }
+  }
+  if constexpr (G == 4) {
+    const float l_tot = l_run[0] + __shfl_xor_sync(0xffffffffu, l_run[0], 16);
+    if (half == 0 && (lane & 3) == 0) {
+      sm_m[warp][lane >> 2] = m_run[0];
+      sm_l[warp][lane >> 2] = l_tot;
+    }
+  } else {
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      const float l_tot = l_run[g] + __shfl_xor_sync(0xffffffffu, l_run[g], 16);
+      if (lane == 0) {
+        sm_m[warp][g] = m_run[g];
+        sm_l[warp][g] = l_tot;
+      }
+    }
+  }
+  __syncthreads();
+
+  for (int idx = threadIdx.x; idx < G * kHeadDim; idx += kDecodeThreads) {
+    const int g = idx / kHeadDim, d = idx % kHeadDim;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kDecodeWarps; ++w) M = fmaxf(M, sm_m[w][g]);
+    const float Ms = (M == -INFINITY) ? 0.f : M;
+    float acc = 0.f, lsum = 0.f;
+#pragma unroll
+    for (int w = 0; w < kDecodeWarps; ++w) {
+      const float wgt = ex2(sm_m[w][g] - Ms);
+      acc += wgt * sm_o[w][g][d];
+      lsum += wgt * sm_l[w][g];
+    }
+    float *dst = partials + (((size_t)b * Hq + hkv * G + g) * n_splits + split) * (kHeadDim + 2);
+    dst[d] = acc;
+    if (d == 0) {
+      dst[kHeadDim] = M;
+      dst[kHeadDim + 1] = lsum;
+    }
+  }
+}
+
+// One warp per output row; lane handles 4 of the 128 elements.
+template <int ODT>
+__global__ void __launch_bounds__(128)
+decode_combine_kernel(const float *__restrict__ partials, void *__restrict__ out, int rows, int n_splits,
+                      long long row_stride, long long split_stride) {
+  const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const float *base = partials + (size_t)row * row_stride;
+  float M = -INFINITY;
+  for (int s = 0; s < n_splits; ++s) M = fmaxf(M, base[(size_t)s * split_stride + kHeadDim]);
+  const float Ms = (M == -INFINITY) ? 0.f : M;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  float lsum = 0.f;
+  for (int s = 0; s < n_splits; ++s) {
+    const float *ps = base + (size_t)s * split_stride;
+    const float w = ex2(ps[kHeadDim] - Ms);
+    const float2 o01 = *reinterpret_cast<const float2 *>(ps + lane * 4);
+    const float2 o23 = *reinterpret_cast<const float2 *>(ps + lane * 4 + 2);
+    acc.x += w * o01.x;
+    acc.y += w * o01.y;
+    acc.z += w * o23.x;
+    acc.w += w * o23.y;
+    lsum += w * ps[kHeadDim + 1];
+  }
+  if constexpr (ODT == NB200_F32) {
+    float *dst = reinterpret_cast<float *>(out) + (size_t)row * (kHeadDim + 2);
+    dst[lane * 4 + 0] = acc.x;
+    dst[lane * 4 + 1] = acc.y;
+    dst[lane * 4 + 2] = acc.z;
+    dst[lane * 4 + 3] = acc.w;
+    if (lane == 0) {
+      dst[kHeadDim] = M;
+      dst[kHeadDim + 1] = lsum;
+    }
+  } else {
+    const float inv = 1.f / lsum;
+    uint2 w;
+    w.x = pack2<ODT>(acc.x * inv, acc.y * inv);
+    w.y = pack2<ODT>(acc.z * inv, acc.w * inv);
+    *reinterpret_cast<uint2 *>(reinterpret_cast<uint16_t *>(out) + (size_t)row * kHeadDim + lane * 4) = w;
+  }
+}
+
+template <int DT>
+int launch_splitk(const void *q, const void *k, const void *v, float *partials, int B, int Hq, int Hkv,
+                  int Lkv, int n_splits, float scale_log2, cudaStream_t st) {
+  const dim3 grid(n_splits, Hkv, B), block(kDecodeThreads);
+  const auto *qp = static_cast<const uint16_t *>(q);
+  const auto *kp = static_cast<const uint16_t *>(k);
+  const auto *vp = static_cast<const uint16_t *>(v);
+  switch (Hq / Hkv) {
+    case 1: decode_splitk_kernel<DT, 1><<<grid, block, 0, st>>>(qp, kp, vp, partials, Hkv, Lkv, n_splits, scale_log2); break;
+    case 2: decode_splitk_kernel<DT, 2><<<grid, block, 0, st>>>(qp, kp, vp, partials, Hkv, Lkv, n_splits, scale_log2); break;
+    case 4: decode_splitk_kernel<DT, 4><<<grid, block, 0, st>>>(qp, kp, vp, partials, Hkv, Lkv, n_splits, scale_log2); break;
+    case 8: decode_splitk_kernel<DT, 8><<<grid, block, 0, st>>>(qp, kp, vp, partials, Hkv, Lkv, n_splits, scale_log2); break;
+    default: return fail(NB200_ERR_UNSUPPORTED, "decode: Hq/Hkv = %d not in {1,2,4,8}", Hq / Hkv);
+  }
+  NB200_CHECK_CUDA(cudaGetLastError());
+  return NB200_OK;
+}
+
+}  // namespace
+}  // namespace nb200
+
+using namespace nb200;
+
+extern "C" size_t nb200_decode_workspace_bytes(int B, int Hq, int D, int n_splits) {
+  if (B <= 0 || Hq <= 0 || D <= 0 || n_splits <= 0) return 0;
+  return (size_t)B * Hq * n_splits * (D + 2) * sizeof(float);
+}
+
+extern "C" int nb200_decode_splitk(const void *q, const void *k, const void *v, float *partials, int B,
+                                   int Hq, int Hkv, int Lkv, int D, int n_splits, int dtype,
+                                   float scale_log2, void *stream) {
+  NB200_REQUIRE(q && k && v && partials, NB200_ERR_BAD_ARG, "decode_splitk: null pointer");
+  NB200_REQUIRE(B > 0 && Hq > 0 && Hkv > 0 && Lkv > 0 && n_splits > 0, NB200_ERR_BAD_ARG,
+                "decode_splitk: non-positive extent");
+  NB200_REQUIRE(aligned16(q) && aligned16(k) && aligned16(v), NB200_ERR_BAD_ARG,
+                "decode_splitk: q/k/v must be 16-byte aligned");
+  NB200_REQUIRE(D == kHeadDim, NB200_ERR_UNSUPPORTED, "decode_splitk: D = %d, only 128 is implemented", D);
+  NB200_REQUIRE(Hq % Hkv == 0, NB200_ERR_UNSUPPORTED, "decode_splitk: Hq %% Hkv != 0");
+  NB200_REQUIRE(Lkv % n_splits == 0 && (Lkv / n_splits) % 16 == 0, NB200_ERR_UNSUPPORTED,
+                "decode_splitk: Lkv/n_splits must be a whole multiple of 16");
+  NB200_REQUIRE(Hkv <= 65535 && B <= 65535, NB200_ERR_UNSUPPORTED, "decode_splitk: grid too large");
+  auto st = static_cast<cudaStream_t>(stream);
+  if (dtype == NB200_BF16) return launch_splitk<NB200_BF16>(q, k, v, partials, B, Hq, Hkv, Lkv, n_splits, scale_log2, st);
+  if (dtype == NB200_F16) return launch_splitk<NB200_F16>(q, k, v, partials, B, Hq, Hkv, Lkv, n_splits, scale_log2, st);
+  return fail(NB200_ERR_UNSUPPORTED, "decode_splitk: dtype %d (f16 and bf16 only)", dtype);
+}
+
+extern "C" int nb200_decode_combine(const float *partials, void *out, int rows, int D, int n_splits,
+                                    long long row_stride, long long split_stride, int out_dtype,
+                                    void *stream) {
+  NB200_REQUIRE(partials && out, NB200_ERR_BAD_ARG, "decode_combine: null pointer");
+  NB200_REQUIRE(rows > 0 && n_splits > 0, NB200_ERR_BAD_ARG, "decode_combine: non-positive extent");
+  NB200_REQUIRE(D == kHeadDim, NB200_ERR_UNSUPPORTED, "decode_combine: D = %d, only 128 is implemented", D);
+  NB200_REQUIRE(row_stride % 2 == 0 && split_stride % 2 == 0 &&
+                    (reinterpret_cast<uintptr_t>(partials) & 7u) == 0,
+                NB200_ERR_BAD_ARG, "decode_combine: partials must be 8-byte aligned with even strides");
+  auto st = static_cast<cudaStream_t>(stream);
+  const dim3 grid((rows + 3) / 4), block(128);
+  switch (out_dtype) {
+    case NB200_BF16: decode_combine_kernel<NB200_BF16><<<grid, block, 0, st>>>(partials, out, rows, n_splits, row_stride, split_stride); break;
+    case NB200_F16: decode_combine_kernel<NB200_F16><<<grid, block, 0, st>>>(partials, out, rows, n_splits, row_stride, split_stride); break;
+    case NB200_F32: decode_combine_kernel<NB200_F32><<<grid, block, 0, st>>>(partials, out, rows, n_splits, row_stride, split_stride); break;
+    default: return fail(NB200_ERR_UNSUPPORTED, "decode_combine: out_dtype %d", out_dtype);
+  }
+  NB200_CHECK_CUDA(cudaGetLastError());
+  return NB200_OK;
+}
