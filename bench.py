@@ -1,0 +1,468 @@
+#!/usr/bin/env python3
+"""Benchmark of the HTile hot path on B200: causal attention prefill (headline), plus split-K decode and both scans.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl native|reference] [--skip-extra]
+
+N > 1 is launched by ``python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...``; the
+work of the fixed configuration is partitioned over ranks by independent units ((batch, head) pairs,
+sequences, channels, heads) with no data-path collective, so the scaling is *strong*.  Rank 0 prints one
+JSON line.  A step is one pass of the workload: one launch of the fused attention kernel over this rank's
+(batch, head) units, called through the function the translator emits for the HTile program.
+
+Timing: CUDA events on the launching stream around every step, L2 flushed (a 512 MB fill) before each
+timed step, a barrier plus device synchronise on both sides of the timed region, maximum over ranks.
+``value`` has its inputs resident in HBM; ``e2e`` runs the same function from pinned host buffers with the
+host-to-device and device-to-host copies inside the timed region.  ``--impl reference`` times the CPU
+restatement of the reference's own check math (the oracle) on the host cores instead.
+"""
+
+from __future__ import annotations
+
+import argparse
+import ast
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+for _p in (str(ROOT), str(ROOT / "mlir-toy_b200")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+
+# ---- the benchmark configurations (BASELINE.json `configs`) ----------------------------------------
+ATTN = dict(B=8, H=32, S=4096, D=128)                       # configs[1]: causal bf16 prefill
+DECODE = dict(B=64, Hq=32, Hkv=8, L=32768, D=128, S=16)     # configs[2]
+DECODE1 = dict(B=1, Hq=32, Hkv=8, L=262144, D=128, S=16)    # configs[2], single-sequence variant
+SCAN = dict(B=8, Dm=4096, L=4096, N=16)                     # configs[3]
+SSD = dict(B=4, L=8192, H=64, P=64, N=128, G=1, chunk=256)  # configs[4]
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+# DRAM bytes per launch of the attention kernel at the full configuration, from the ncu capture
+# summarised in profiles/ (None until a capture has been taken).
+ATTN_DRAM_TRAFFIC_BYTES = None
+
+
+def attn_flops(units: int, S: int, D: int) -> float:
+    """4*D FLOP per unmasked (i, j) pair: 2*D*S*(S+1) per (batch, head) unit."""
+    return 2.0 * units * D * S * (S + 1)
+
+
+def peaks() -> tuple[dict, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        return json.loads(path.read_text()), "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+def load_callable(text: str, fn_name: str):
+    """HTile text -> emitted module -> the function named after the func.func."""
+    from neptune_mlir.translators import b200
+
+    with tempfile.NamedTemporaryFile("w", suffix=".mlir", delete=False) as f:
+        f.write(text)
+    ns: dict = {}
+    exec(compile(ast.unparse(b200.translate_file(f.name)), f"<nb200 {fn_name}>", "exec"), ns)
+    os.unlink(f.name)
+    return ns[fn_name]
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self) -> dict:
+        sm, mx, reasons = [], [], set()
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) != 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(self.NAMES, parts[2:]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+class Dist:
+    def __init__(self, n_gpus: int):
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        if self.world != n_gpus:
+            if self.world == 1 and n_gpus > 1:
+                raise SystemExit(f"--gpus {n_gpus} needs a torchrun launch with {n_gpus} ranks")
+            raise SystemExit(f"--gpus {n_gpus} but WORLD_SIZE={self.world}")
+        if self.world > 1 and not dist.is_initialized():
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            dist.init_process_group("nccl", device_id=torch.device("cuda", self.local_rank))
+
+    def barrier(self):
+        if self.world > 1:
+            dist.barrier()
+
+    def max(self, x: float) -> float:
+        if self.world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+
+def timed_steps(fn, steps: int, warmup: int, flush: torch.Tensor, d: Dist) -> float:
+    """Mean milliseconds per step over `steps` timed calls (max over ranks), L2 flushed before each."""
+    for _ in range(warmup):
+        flush.fill_(1.0)
+        fn()
+    torch.cuda.synchronize()
+    d.barrier()
+    torch.cuda.synchronize()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    for i in range(steps):
+        flush.fill_(float(i))
+        starts[i].record()
+        fn()
+        ends[i].record()
+    torch.cuda.synchronize()
+    d.barrier()
+    torch.cuda.synchronize()
+    total = sum(s.elapsed_time(e) for s, e in zip(starts, ends))
+    return d.max(total) / steps
+
+
+# ---- CPU arm ---------------------------------------------------------------------------------------
+def cpu_attention_sample(heads: int) -> tuple[float, float]:
+    """Times the oracle (the reference's check math + causal mask) on `heads` (batch, head) units of the
+    attention configuration; returns (seconds, TFLOP/s counting the causal FLOPs)."""
+    from oracle import attention, inputs
+
+    S, D = ATTN["S"], ATTN["D"]
+    q, k, v = inputs.attention_inputs(1, heads, S, D, torch.bfloat16, config=2)
+    t0 = time.perf_counter()
+    attention.attention_reference(q, k, v, causal=True)
+    dt = time.perf_counter() - t0
+    return dt, attn_flops(heads, S, D) / dt / 1e12
+
+
+def run_reference_arm(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    torch.set_num_threads(os.cpu_count() or 1)
+    heads = 8  # per step: a bounded sample of the configuration (8 of its 256 (batch, head) units)
+    for _ in range(args.warmup):
+        cpu_attention_sample(heads)
+    secs = [cpu_attention_sample(heads)[0] for _ in range(args.steps)]
+    mean = sum(secs) / len(secs)
+    value = attn_flops(heads, ATTN["S"], ATTN["D"]) / mean / 1e12
+    sample = f"{heads} of {ATTN['B'] * ATTN['H']} (batch, head) units per step, full S={ATTN['S']}"
+    print(json.dumps({
+        "impl": "reference", "metric": "attn_prefill_tflops", "value": value, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": mean * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": attn_config(args.gpus) | {"sample": sample},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def attn_config(n: int) -> dict:
+    return {"workload": "causal attention prefill bf16 B=8 H=32 S=4096 D=128 (configs[1])",
+            "global_batch": ATTN["B"], "heads": ATTN["H"], "seq_len": ATTN["S"], "head_dim": ATTN["D"],
+            "partition": f"(batch, head) units over {n} rank(s), no collective",
+            "l2": "flushed before every timed step (512 MB fill)",
+            "flop_count": "2*B*H*D*S*(S+1) (unmasked pairs only)"}
+
+
+# ---- GPU arm ---------------------------------------------------------------------------------------
+def bench_attention(args, d: Dist, dev, flush, pk, pk_kind) -> dict:
+    from neptune_mlir import programs, runtime
+    from neptune_mlir.sharding import shard_range
+
+    S, D = ATTN["S"], ATTN["D"]
+    total_units = ATTN["B"] * ATTN["H"]
+    lo, hi = shard_range(total_units, d.rank, d.world)
+    units = hi - lo
+    fn = load_callable(programs.attention_htile("attention_prefill", units, 1, S, D, "bf16", causal=True), "attention_prefill")
+    gen = torch.Generator(device=dev).manual_seed(2000 + d.rank)
+    q, k, v = (torch.randn((units, 1, S, D), device=dev, dtype=torch.bfloat16, generator=gen) for _ in range(3))
+    out = torch.empty_like(q)
+
+    with ClockSampler(dev.index) as clocks:
+        ms = timed_steps(lambda: fn(q, k, v, out), args.steps, args.warmup, flush, d)
+    runtime.check_status(dev)
+    flops_total = attn_flops(total_units, S, D)
+    value = flops_total / (ms * 1e-3) / 1e12
+    # roofline of the dominant (only) kernel, per launch on this rank
+    achieved = attn_flops(units, S, D) / (ms * 1e-3) / 1e12
+    peak = pk["bf16_tflops"]
+    result = {
+        "ms": ms, "value": value, "clocks": clocks.summary(),
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                     "traffic": ATTN_DRAM_TRAFFIC_BYTES, "peak_source": f"of {pk_kind} (burst cuBLAS bf16)",
+                     "kernel": "attn_fwd_tcgen05_kernel<bf16>"},
+    }
+
+    # ---- end to end: pinned host buffers, copies inside the timed region, chunked so that copies overlap compute
+    chunk_units = max(1, units // 8)
+    while units % chunk_units:
+        chunk_units -= 1
+    n_chunks = units // chunk_units
+    fn_chunk = load_callable(programs.attention_htile("attention_chunk", chunk_units, 1, S, D, "bf16", causal=True),
+                             "attention_chunk")
+    hq, hk, hv = (t.cpu().pin_memory() for t in (q, k, v))
+    hout = torch.empty((units, 1, S, D), dtype=torch.bfloat16).pin_memory()
+    dq, dk, dv, dout = (torch.empty_like(q) for _ in range(4))
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+
+    def e2e_step():
+        main = torch.cuda.current_stream(dev)
+        s_in.wait_stream(main)
+        s_out.wait_stream(main)
+        for c in range(n_chunks):
+            sl = slice(c * chunk_units, (c + 1) * chunk_units)
+            with torch.cuda.stream(s_in):
+                dq[sl].copy_(hq[sl], non_blocking=True)
+                dk[sl].copy_(hk[sl], non_blocking=True)
+                dv[sl].copy_(hv[sl], non_blocking=True)
+                ready = torch.cuda.Event()
+                ready.record(s_in)
+            main.wait_event(ready)
+            fn_chunk(dq[sl], dk[sl], dv[sl], dout[sl])
+            done = torch.cuda.Event()
+            done.record(main)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(done)
+                hout[sl].copy_(dout[sl], non_blocking=True)
+        main.wait_stream(s_out)
+
+    e2e_steps = max(2, min(args.steps, 5))
+    ms_e2e = timed_steps(e2e_step, e2e_steps, 1, flush, d)
+    runtime.check_status(dev)
+    elem = 2
+    result["e2e"] = {"value": flops_total / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
+                     "h2d_bytes_per_step": 3 * units * S * D * elem, "d2h_bytes_per_step": units * S * D * elem,
+                     "ms_per_step": ms_e2e, "steps": e2e_steps,
+                     "how": f"{n_chunks} chunks of {chunk_units} units through the emitted function; H2D, kernel and "
+                            "D2H on three streams from/to pinned host memory"}
+    result["gpu_launches"] = args.steps
+    del q, k, v, out, dq, dk, dv, dout
+    torch.cuda.empty_cache()
+    return result
+
+
+def bench_extra(args, d: Dist, dev, flush, pk, pk_kind) -> dict:
+    """Decode and both scans at their configurations (HBM-bound by the metric): GB/s of algorithmic bytes."""
+    from neptune_mlir import programs, runtime
+    from neptune_mlir.sharding import gather_partials, gathered_strides, shard_range
+
+    steps, warm = max(3, min(args.steps, 10)), 3
+    hbm = pk["hbm_gbs"]
+    out: dict = {}
+    gen = torch.Generator(device=dev).manual_seed(3000 + d.rank)
+    bf = torch.bfloat16
+
+    def rnd(shape, dtype=bf):
+        return torch.randn(shape, device=dev, dtype=dtype, generator=gen)
+
+    def record(name, ms, total_bytes, extra=None):
+        gbs = total_bytes / (ms * 1e-3) / 1e9
+        out[name] = {"ms_per_step": ms, "value": gbs, "unit": "GB/s", "algorithmic_bytes": total_bytes,
+                     "roofline": {"bound": "hbm", "achieved": gbs / d.world, "peak": hbm, "unit": "GB/s",
+                                  "frac": gbs / d.world / hbm, "peak_source": f"of {pk_kind} (copy)"}} | (extra or {})
+
+    # -- split-K decode, batch sharded over ranks
+    c = DECODE
+    lo, hi = shard_range(c["B"], d.rank, d.world)
+    Bl = hi - lo
+    fn = load_callable(programs.decode_splitk_decl("decode", Bl, c["Hq"], c["Hkv"], c["L"], c["D"], c["S"]), "decode")
+    q, k, v = rnd((Bl, c["Hq"], c["D"])), rnd((Bl, c["Hkv"], c["L"], c["D"])), rnd((Bl, c["Hkv"], c["L"], c["D"]))
+    part = torch.empty((Bl, c["Hq"], c["S"], c["D"] + 2), device=dev)
+    o = torch.empty_like(q)
+    ms = timed_steps(lambda: fn(q, k, v, part, o), steps, warm, flush, d)
+    total = 2 * c["B"] * c["Hkv"] * c["L"] * c["D"] * 2 + 2 * c["B"] * c["Hq"] * c["D"] * 2
+    record("decode_splitk", ms, total, {"config": "B=64 Hq=32 Hkv=8 L=32768 D=128, 16 splits (configs[2])", "launches_per_step": 2})
+    del q, k, v, part, o
+    torch.cuda.empty_cache()
+
+    # -- single sequence, KV sharded along L over ranks, partials merged over NCCL
+    c = DECODE1
+    lo, hi = shard_range(c["L"], d.rank, d.world)
+    Ll = hi - lo
+    rows = c["Hq"]
+    q = rnd((1, c["Hq"], c["D"]))
+    if d.world > 1:
+        dist.broadcast(q, src=0)
+    k, v = rnd((1, c["Hkv"], Ll, c["D"])), rnd((1, c["Hkv"], Ll, c["D"]))
+    part = torch.empty((1, c["Hq"], c["S"], c["D"] + 2), device=dev)
+    local = torch.empty((rows, c["D"] + 2), device=dev)
+    o = torch.empty((rows, c["D"]), device=dev, dtype=bf)
+    scale_log2 = math.log2(math.e) / math.sqrt(c["D"])
+    from neptune_mlir import native
+    lib = native.lib()
+
+    def stream_part():
+        st = torch.cuda.current_stream(dev).cuda_stream
+        native.check(lib.nb200_decode_splitk(q.data_ptr(), k.data_ptr(), v.data_ptr(), part.data_ptr(), 1, c["Hq"], c["Hkv"],
+                                             Ll, c["D"], c["S"], 1, scale_log2, st), "decode_splitk")
+        runtime.decode_combine(part, local, rows=rows, D=c["D"], n_splits=c["S"], row_stride=c["S"] * (c["D"] + 2),
+                               split_stride=c["D"] + 2, out_dtype="f32")
+
+    def merge_part():
+        if d.world > 1:
+            g = gather_partials(local)
+            rs, ss = gathered_strides(rows, c["D"] + 2)
+            runtime.decode_combine(g, o, rows=rows, D=c["D"], n_splits=d.world, row_stride=rs, split_stride=ss, out_dtype="bf16")
+        else:
+            runtime.decode_combine(local, o, rows=rows, D=c["D"], n_splits=1, row_stride=c["D"] + 2,
+                                   split_stride=c["D"] + 2, out_dtype="bf16")
+
+    ms_stream = timed_steps(stream_part, steps, warm, flush, d)
+    ms_merge = timed_steps(merge_part, steps, warm, flush, d)
+    ms_both = timed_steps(lambda: (stream_part(), merge_part()), steps, warm, flush, d)
+    total = 2 * c["Hkv"] * c["L"] * c["D"] * 2 + 2 * c["Hq"] * c["D"] * 2
+    record("decode_single_sequence", ms_both, total,
+           {"config": "B=1 L=262144 KV sharded along L over ranks (configs[2] variant)", "stream_ms": ms_stream,
+            "merge_ms": ms_merge, "merge_bytes_per_rank": rows * (c["D"] + 2) * 4,
+            "collective": "all_gather (NCCL)" if d.world > 1 else "none"})
+    del q, k, v, part, local, o
+    torch.cuda.empty_cache()
+
+    # -- Mamba-1 selective scan, (batch x channel) rows sharded as whole sequences when possible, else channels
+    c = SCAN
+    if c["B"] % d.world == 0:
+        Bl, Dl = c["B"] // d.world, c["Dm"]
+    else:
+        Bl, Dl = c["B"], c["Dm"] // d.world
+    fn = load_callable(programs.selective_scan_decl("scan", Bl, Dl, c["L"], c["N"]), "scan")
+    u, z = rnd((Bl, Dl, c["L"])), rnd((Bl, Dl, c["L"]))
+    delta = torch.nn.functional.softplus(rnd((Bl, Dl, c["L"]), torch.float32) - 4.0).to(bf)
+    A = -torch.exp(torch.rand((Dl, c["N"]), device=dev, generator=gen) * math.log(16.0))
+    Bm, Cm = rnd((Bl, c["N"], c["L"])), rnd((Bl, c["N"], c["L"]))
+    Dk = rnd((Dl,), torch.float32)
+    o = torch.empty_like(u)
+    ms = timed_steps(lambda: fn(u, delta, A, Bm, Cm, Dk, z, o), steps, warm, flush, d)
+    total = 4 * c["B"] * c["Dm"] * c["L"] * 2 + 2 * c["B"] * c["N"] * c["L"] * 2 + c["Dm"] * c["N"] * 4 + c["Dm"] * 4
+    record("selective_scan", ms, total, {"config": "B=8 D=4096 L=4096 N=16 (configs[3])", "launches_per_step": 1,
+                                         "state_updates_per_s": c["B"] * c["Dm"] * c["L"] * c["N"] / (ms * 1e-3)})
+    del u, z, delta, A, Bm, Cm, Dk, o
+    torch.cuda.empty_cache()
+
+    # -- Mamba-2 SSD, heads sharded over ranks
+    c = SSD
+    lo, hi = shard_range(c["H"], d.rank, d.world)
+    Hl = hi - lo
+    ws_bytes = runtime.ssd_workspace_bytes(c["B"], c["L"], Hl, c["P"], c["N"], c["G"], c["chunk"])
+    fn = load_callable(programs.ssd_chunk_scan_decl("ssd", c["B"], c["L"], Hl, c["P"], c["N"], c["G"], c["chunk"], ws_bytes), "ssd")
+    x = rnd((c["B"], c["L"], Hl, c["P"]))
+    dt = torch.nn.functional.softplus(rnd((c["B"], c["L"], Hl), torch.float32))
+    A = -torch.exp(torch.rand((Hl,), device=dev, generator=gen) * math.log(16.0))
+    Bm, Cm = rnd((c["B"], c["L"], c["G"], c["N"])), rnd((c["B"], c["L"], c["G"], c["N"]))
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+    y = torch.empty_like(x)
+    ms = timed_steps(lambda: fn(x, dt, A, Bm, Cm, ws, y), steps, warm, flush, d)
+    total = 2 * c["B"] * c["L"] * c["H"] * c["P"] * 2 + c["B"] * c["L"] * c["H"] * 4 + 2 * c["B"] * c["L"] * c["G"] * c["N"] * 2 + c["H"] * 4
+    record("ssd_chunk_scan", ms, total, {"config": "B=4 L=8192 H=64 P=64 N=128 chunk=256 (configs[4])", "launches_per_step": 3})
+    return out
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=("native", "reference"), default="native")
+    ap.add_argument("--skip-extra", action="store_true", help="attention only (skip decode and the scans)")
+    ap.add_argument("--skip-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "native" else args.warmup
+
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py measures CUDA kernels; no CUDA device is visible (there is no CPU fallback)")
+    d = Dist(args.gpus)
+    dev = torch.device("cuda", d.local_rank)
+    torch.cuda.set_device(dev)
+    pk, pk_kind = peaks()
+    flush = torch.empty(128 * 1024 * 1024, dtype=torch.float32, device=dev)  # 512 MB > L2
+
+    cpu = None
+    if d.rank == 0 and not args.skip_cpu:
+        torch.set_num_threads(os.cpu_count() or 1)
+        heads = 128
+        cpu_attention_sample(2)  # warm the thread pool
+        secs, tf = cpu_attention_sample(heads)
+        cpu = {"value": tf, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port", "seconds": secs,
+               "sample": f"{heads} of {ATTN['B'] * ATTN['H']} (batch, head) units of the configuration, full S, "
+                         "oracle attention_reference (the reference's check math plus the causal mask) on CPU tensors"}
+    d.barrier()
+
+    attn = bench_attention(args, d, dev, flush, pk, pk_kind)
+    extra = {} if args.skip_extra else bench_extra(args, d, dev, flush, pk, pk_kind)
+
+    if d.rank == 0:
+        line = {
+            "metric": "attn_prefill_tflops", "value": attn["value"], "unit": "TFLOP/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": attn["ms"], "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": attn_config(args.gpus), "roofline": attn["roofline"], "cpu_baseline": cpu, "e2e": attn["e2e"],
+            "gpu_launches": attn["gpu_launches"], "clocks": attn["clocks"], "workloads": extra,
+        }
+        print(json.dumps(line))
+    if d.world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,65 @@
+"""Helpers shared by the GPU parity tests."""
+
+import ast
+import importlib.util
+import sys
+import tempfile
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parents[1]
+DATA = ROOT / "tests" / "data"
+
+
+def exec_translated_module(module_ast: ast.Module, module_name: str):
+    """Write the emitted module to a file and import it, as tests/test_translators.py:86-103 of the reference does."""
+    source = ast.unparse(module_ast) + "\n"
+    with tempfile.NamedTemporaryFile(mode="w", suffix=".py", prefix=f"{module_name}_", delete=False) as f:
+        f.write(source)
+        module_path = Path(f.name)
+    spec = importlib.util.spec_from_file_location(module_name, module_path)
+    module = importlib.util.module_from_spec(spec)
+    sys.modules[module_name] = module
+    spec.loader.exec_module(module)
+    return module
+
+
+def translate_text(text: str, module_name: str):
+    from neptune_mlir.translators import b200
+
+    with tempfile.NamedTemporaryFile(mode="w", suffix=".mlir", delete=False) as f:
+        f.write(text)
+        path = f.name
+    return exec_translated_module(b200.translate_file(path), module_name)
+
+
+def translate_data(stem: str):
+    from neptune_mlir.translators import b200
+
+    return exec_translated_module(b200.translate_file(str(DATA / f"{stem}.mlir")), f"translated_{stem}")
+
+
+def finish(device=None):
+    """Synchronise and fail if any kernel reported an expired device-side wait."""
+    from neptune_mlir import runtime
+
+    torch.cuda.synchronize()
+    runtime.check_status(device)
+
+
+def assert_storage_close(out: torch.Tensor, ref: torch.Tensor, atol: float, rel_ulp: float = 0.0):
+    """|out - ref| <= atol + rel_ulp*|ref| element-wise, on CPU in fp32.
+
+    ``rel_ulp`` is used only for the scans, whose outputs reach magnitudes where one unit in the
+    last place of a 16-bit float exceeds the absolute tolerance (a bf16 ulp at 32 is 0.25), so that
+    even the correctly rounded result misses a purely absolute bound.
+    """
+    out = out.detach().float().cpu()
+    ref = ref.detach().float().cpu()
+    assert out.shape == ref.shape
+    assert bool(torch.isfinite(out).all()), "output has non-finite values"
+    err = (out - ref).abs()
+    bound = atol + rel_ulp * ref.abs()
+    worst = (err - bound).max().item()
+    assert worst <= 0, f"max abs err {err.max().item():.3e}; worst excess over bound {worst:.3e}"

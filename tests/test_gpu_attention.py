@@ -1,0 +1,131 @@
+"""GPU parity of the attention path, called through the translator's emitted module and the C ABI."""
+
+import math
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from gpu_util import assert_storage_close, finish, translate_data, translate_text
+from oracle import attention, inputs
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = Path(__file__).parent / "golden" / "flash_attention_ref_tiles.npz"
+BF16_ATOL = 2e-2   # max-abs-error bound for bf16 outputs
+F32_ATOL = 1e-4    # max-abs-error bound for fp32 outputs
+REF_F16_ATOL = 1e-3  # the reference's own bound for its f16 program (tests/test_translators.py:143)
+
+
+def test_reference_shape_f16_matches_reference_golden_tiles(cuda, native_lib):
+    """Non-causal f16 1x32x4096x128: the reference's problem, checked against tiles its own kernel produced."""
+    g = np.load(GOLDEN)
+    shape = tuple(int(s) for s in g["shape"])
+    q, k, v = inputs.attention_inputs(*shape, torch.float16, config=0)
+    mod = translate_data("attention_f16_1x32x4096x128")
+    qd, kd, vd = q.to(cuda), k.to(cuda), v.to(cuda)
+    out = torch.full(shape, float("nan"), dtype=torch.float16, device=cuda)
+    mod.attention_f16(qd, kd, vd, out)
+    finish()
+    assert tuple(out.shape) == shape and out.dtype == torch.float16
+    assert bool(torch.isfinite(out).all())
+    for (head, blk), tile in zip(g["programs"], g["tiles"]):
+        r0 = int(blk) * 128
+        got = out[0, head, r0:r0 + 128].float().cpu()
+        torch.testing.assert_close(got, torch.from_numpy(tile).float(), rtol=0, atol=REF_F16_ATOL)
+    # and against the restated check function of the reference on a few whole heads
+    for head in (3, 30):
+        ref = attention.attention_reference(q[:, head:head + 1], k[:, head:head + 1], v[:, head:head + 1])
+        torch.testing.assert_close(out[:, head:head + 1].float().cpu(), ref, rtol=0, atol=REF_F16_ATOL)
+
+
+def test_config1_fp32_causal(cuda, native_lib):
+    """B=1, H=4, S=256, D=64 fp32 causal (exact-fp32 kernel)."""
+    q, k, v = inputs.attention_inputs(1, 4, 256, 64, torch.float32, config=1)
+    mod = translate_data("attention_causal_f32_1x4x256x64")
+    out = torch.full((1, 4, 256, 64), float("nan"), device=cuda)
+    mod.attention_causal_f32(q.to(cuda), k.to(cuda), v.to(cuda), out)
+    finish()
+    assert_storage_close(out, attention.attention_reference(q, k, v, causal=True), F32_ATOL)
+
+
+@pytest.mark.parametrize("dtype,name,atol", [(torch.bfloat16, "bf16", BF16_ATOL), (torch.float16, "f16", 2e-3)])
+@pytest.mark.parametrize("causal", [False, True])
+def test_tensor_core_path_small(cuda, native_lib, dtype, name, atol, causal):
+    """Ragged work per tile (1..4 kv blocks), several heads; every element against the oracle."""
+    from neptune_mlir import programs
+
+    B, H, S, D = 2, 3, 512, 128
+    q, k, v = inputs.attention_inputs(B, H, S, D, dtype, config=2)
+    mod = translate_text(programs.attention_htile("attn_small", B, H, S, D, name, causal=causal),
+                         f"attn_small_{name}_{int(causal)}")
+    out = torch.full((B, H, S, D), float("nan"), dtype=dtype, device=cuda)
+    mod.attn_small(q.to(cuda), k.to(cuda), v.to(cuda), out)
+    finish()
+    assert_storage_close(out, attention.attention_reference(q, k, v, causal=causal), atol)
+    # the program-faithful oracle (P rounded before PV, exp2 domain) is matched at least as well
+    assert_storage_close(out, attention.attention_program(q, k, v, causal=causal), atol)
+
+
+def test_single_tile_and_determinism(cuda, native_lib):
+    from neptune_mlir import runtime
+
+    q, k, v = (t.to(cuda) for t in inputs.attention_inputs(1, 1, 128, 128, torch.bfloat16, config=2))
+    outs = []
+    for _ in range(2):
+        out = torch.empty_like(q)
+        runtime.attn_fwd(q, k, v, out, shape=(1, 1, 128, 128), kv_len=128, dtype="bf16",
+                         scale_log2=attention.scale_log2(128), causal=True)
+        finish()
+        outs.append(out)
+    assert torch.equal(outs[0], outs[1])
+    ref = attention.attention_reference(q.cpu(), k.cpu(), v.cpu(), causal=True)
+    assert_storage_close(outs[0], ref, BF16_ATOL)
+    torch.testing.assert_close(outs[0][0, 0, 0].float(), v[0, 0, 0].float())  # row 0 sees only key 0
+
+
+def test_causal_with_longer_kv_and_large_scores(cuda, native_lib):
+    """Skv > Sq (diagonal offset) and scores scaled up so that row maxima move by more than the rescale threshold."""
+    from neptune_mlir import runtime
+
+    B, H, Sq, Skv, D = 1, 2, 256, 512, 128
+    q, k, v = inputs.attention_inputs(B, H, Sq, D, torch.bfloat16, config=2, Skv=Skv)
+    q = (q.float() * 6).to(torch.bfloat16)
+    out = torch.empty((B, H, Sq, D), dtype=torch.bfloat16, device=cuda)
+    runtime.attn_fwd(q.to(cuda), k.to(cuda), v.to(cuda), out, shape=(B, H, Sq, D), kv_len=Skv, dtype="bf16",
+                     scale_log2=attention.scale_log2(D), causal=True)
+    finish()
+    assert_storage_close(out, attention.attention_reference(q, k, v, causal=True), BF16_ATOL)
+
+
+def test_config2_full_size_sampled(cuda, native_lib):
+    """B=8, H=32, S=4096, D=128 bf16 causal; sampled (batch, head, row block) tiles against the oracle."""
+    B, H, S, D = 8, 32, 4096, 128
+    gen = torch.Generator(device=cuda).manual_seed(2000)
+    q, k, v = (torch.randn((B, H, S, D), device=cuda, dtype=torch.bfloat16, generator=gen) for _ in range(3))
+    mod = translate_data("attention_causal_bf16_8x32x4096x128")
+    out = torch.full((B, H, S, D), float("nan"), dtype=torch.bfloat16, device=cuda)
+    mod.attention_causal_bf16(q, k, v, out)
+    finish()
+    assert bool(torch.isfinite(out).all())
+    for b, h, blk in ((0, 0, 0), (0, 0, 31), (3, 17, 7), (7, 31, 31), (5, 9, 16)):
+        r0 = blk * 128
+        qs = q[b:b + 1, h:h + 1, r0:r0 + 128].cpu()
+        ks, vs = k[b:b + 1, h:h + 1, :r0 + 128].cpu(), v[b:b + 1, h:h + 1, :r0 + 128].cpu()
+        ref = attention.attention_reference(qs, ks, vs, causal=True)  # Skv - Sq offset = r0 puts the tile on the diagonal
+        assert_storage_close(out[b:b + 1, h:h + 1, r0:r0 + 128], ref, BF16_ATOL)
+    # softmax rows are convex combinations of V rows: outputs stay inside V's range
+    assert out.float().abs().max() <= v.float().abs().max() + 1e-2
+
+
+def test_runtime_checks_tensors_against_the_program(cuda, native_lib):
+    mod = translate_data("attention_causal_f32_1x4x256x64")
+    good = torch.zeros((1, 4, 256, 64), device=cuda)
+    with pytest.raises(ValueError, match="shape"):
+        mod.attention_causal_f32(good, good, good[:, :2], good)
+    with pytest.raises(TypeError, match="dtype"):
+        mod.attention_causal_f32(good, good, good.half(), good)
+    strided = torch.zeros((1, 4, 256, 128), device=cuda)[..., ::2]
+    with pytest.raises(ValueError, match="contiguous"):
+        mod.attention_causal_f32(good, good, strided, good)

@@ -1,0 +1,166 @@
+"""GPU parity of split-K decode, the Mamba-1 selective scan and the Mamba-2 SSD scan."""
+
+import math
+
+import pytest
+import torch
+
+from gpu_util import assert_storage_close, finish, translate_data, translate_text
+from oracle import decode, inputs, selective_scan, ssd
+
+pytestmark = pytest.mark.gpu
+
+BF16_ATOL = 2e-2
+BF16_ULP = 2.0 ** -8   # one bf16 unit in the last place, relative
+LOG2E = math.log2(math.e)
+
+
+# ------------------------------------------------------------------ decode
+@pytest.mark.parametrize("Hq,Hkv", [(8, 2), (4, 4), (4, 2), (8, 1)])
+def test_decode_small_all_group_sizes(cuda, native_lib, Hq, Hkv):
+    from neptune_mlir import programs
+
+    B, L, D, S = 2, 1024, 128, 4
+    q, k, v = inputs.decode_inputs(B=B, Hq=Hq, Hkv=Hkv, L=L, D=D)
+    mod = translate_text(programs.decode_splitk_decl("dec", B, Hq, Hkv, L, D, S), f"dec_{Hq}_{Hkv}")
+    partials = torch.full((B, Hq, S, D + 2), float("nan"), device=cuda)
+    out = torch.full((B, Hq, D), float("nan"), dtype=torch.bfloat16, device=cuda)
+    mod.dec(q.to(cuda), k.to(cuda), v.to(cuda), partials, out)
+    finish()
+    assert_storage_close(out, decode.decode_reference(q, k, v), BF16_ATOL)
+    # per-split partials against the oracle's split form (kernel keeps m in the exp2 domain)
+    m, l, o = decode.decode_partials(q, k, v, S)
+    p = partials.cpu()
+    torch.testing.assert_close(p[..., D], m * LOG2E, rtol=1e-4, atol=1e-3)
+    torch.testing.assert_close(p[..., D + 1], l, rtol=1e-3, atol=1e-3)
+    torch.testing.assert_close(p[..., :D], o, rtol=1e-3, atol=2e-3)
+
+
+def test_decode_ragged_split_and_f16(cuda, native_lib):
+    """Split length 48 is not a multiple of the 64-row CTA step: the tail rows are masked."""
+    from neptune_mlir import runtime
+
+    B, Hq, Hkv, L, D, S = 1, 8, 2, 192, 128, 4
+    q, k, v = inputs.decode_inputs(B=B, Hq=Hq, Hkv=Hkv, L=L, D=D, dtype=torch.float16)
+    partials = torch.empty((B, Hq, S, D + 2), device=cuda)
+    out = torch.empty((B, Hq, D), dtype=torch.float16, device=cuda)
+    runtime.decode_splitk(q.to(cuda), k.to(cuda), v.to(cuda), partials, out, B=B, Hq=Hq, Hkv=Hkv, L=L, D=D,
+                          n_splits=S, dtype="f16", scale_log2=LOG2E / math.sqrt(D))
+    finish()
+    assert_storage_close(out, decode.decode_reference(q, k, v), 2e-3)
+
+
+def test_combine_with_gather_strides_and_partial_output(cuda, native_lib):
+    """The cross-GPU merge: per-rank partials laid out [rank, rows, D+2] merge to the same answer."""
+    from neptune_mlir import runtime
+    from neptune_mlir.sharding import gathered_strides
+
+    B, Hq, Hkv, L, D, R = 1, 8, 2, 2048, 128, 4
+    q, k, v = inputs.decode_inputs(B=B, Hq=Hq, Hkv=Hkv, L=L, D=D)
+    qd = q.to(cuda)
+    per_rank = []
+    for r in range(R):                                     # each "rank" owns a quarter of the sequence
+        ks = k[:, :, r * L // R:(r + 1) * L // R].contiguous().to(cuda)
+        vs = v[:, :, r * L // R:(r + 1) * L // R].contiguous().to(cuda)
+        partials = torch.empty((B, Hq, 2, D + 2), device=cuda)
+        tmp = torch.empty((B, Hq, D), dtype=torch.bfloat16, device=cuda)
+        runtime.decode_splitk(qd, ks, vs, partials, tmp, B=B, Hq=Hq, Hkv=Hkv, L=L // R, D=D, n_splits=2,
+                              dtype="bf16", scale_log2=LOG2E / math.sqrt(D))
+        local = torch.empty((B * Hq, D + 2), device=cuda)
+        runtime.decode_combine(partials, local, rows=B * Hq, D=D, n_splits=2, row_stride=2 * (D + 2),
+                               split_stride=D + 2, out_dtype="f32")
+        per_rank.append(local)
+    gathered = torch.stack(per_rank)                       # what an all-gather delivers
+    rs, ss = gathered_strides(B * Hq, D + 2)
+    out = torch.empty((B * Hq, D), dtype=torch.bfloat16, device=cuda)
+    runtime.decode_combine(gathered, out, rows=B * Hq, D=D, n_splits=R, row_stride=rs, split_stride=ss,
+                           out_dtype="bf16")
+    finish()
+    assert_storage_close(out.view(B, Hq, D), decode.decode_reference(q, k, v), BF16_ATOL)
+
+
+def test_decode_config3_full_size_sampled(cuda, native_lib):
+    """B=64, Hq=32, Hkv=8, L=32768, D=128, 16 splits; sampled sequences against the oracle."""
+    B, Hq, Hkv, L, D, S = 64, 32, 8, 32768, 128, 16
+    gen = torch.Generator(device=cuda).manual_seed(3000)
+    q = torch.randn((B, Hq, D), device=cuda, dtype=torch.bfloat16, generator=gen)
+    k = torch.randn((B, Hkv, L, D), device=cuda, dtype=torch.bfloat16, generator=gen)
+    v = torch.randn((B, Hkv, L, D), device=cuda, dtype=torch.bfloat16, generator=gen)
+    mod = translate_data("decode_splitk_bf16_64x32x8x32768x128")
+    partials = torch.full((B, Hq, S, D + 2), float("nan"), device=cuda)
+    out = torch.full((B, Hq, D), float("nan"), dtype=torch.bfloat16, device=cuda)
+    mod.decode_splitk_bf16(q, k, v, partials, out)
+    finish()
+    assert bool(torch.isfinite(out).all())
+    for b in (0, 31, 63):
+        ref = decode.decode_reference(q[b:b + 1].cpu(), k[b:b + 1].cpu(), v[b:b + 1].cpu())
+        assert_storage_close(out[b:b + 1], ref, BF16_ATOL)
+    del k, v
+    torch.cuda.empty_cache()
+
+
+# ------------------------------------------------------------------ Mamba-1
+@pytest.mark.parametrize("dtype,name", [(torch.bfloat16, "bf16"), (torch.float16, "f16")])
+def test_selective_scan_small(cuda, native_lib, dtype, name):
+    from neptune_mlir import programs
+
+    B, Dm, L, N = 2, 64, 256, 16
+    args = inputs.selective_scan_inputs(B=B, Dm=Dm, L=L, N=N, dtype=dtype)
+    mod = translate_text(programs.selective_scan_decl("scan", B, Dm, L, N, name), f"scan_{name}")
+    out = torch.full((B, Dm, L), float("nan"), dtype=dtype, device=cuda)
+    mod.scan(*(a.to(cuda) for a in args), out)
+    finish()
+    ref = selective_scan.selective_scan_reference(*args)
+    assert_storage_close(out, ref, BF16_ATOL if dtype == torch.bfloat16 else 4e-3,
+                         BF16_ULP if dtype == torch.bfloat16 else 2.0 ** -10)
+
+
+def test_selective_scan_config4_full_size_sampled(cuda, native_lib):
+    """B=8, D=4096, L=4096, N=16: channels are independent, so a sample of them is checked in full."""
+    B, Dm, L, N = 8, 4096, 4096, 16
+    u, delta, A, Bm, Cm, Dk, z = (a.to(cuda) for a in inputs.selective_scan_inputs(B=B, Dm=Dm, L=L, N=N))
+    mod = translate_data("selective_scan_bf16_8x4096x4096")
+    out = torch.full((B, Dm, L), float("nan"), dtype=torch.bfloat16, device=cuda)
+    mod.selective_scan_bf16(u, delta, A, Bm, Cm, Dk, z, out)
+    finish()
+    assert bool(torch.isfinite(out).all())
+    ch = torch.tensor([0, 1, 31, 32, 2047, 4095], device=cuda)
+    ref = selective_scan.selective_scan_reference(
+        u[:, ch].cpu(), delta[:, ch].cpu(), A[ch].cpu(), Bm.cpu(), Cm.cpu(), Dk[ch].cpu(), z[:, ch].cpu())
+    assert_storage_close(out[:, ch], ref, BF16_ATOL, BF16_ULP)
+
+
+# ------------------------------------------------------------------ Mamba-2
+@pytest.mark.parametrize("chunk", [64, 128, 256])
+@pytest.mark.parametrize("G", [1, 2])
+def test_ssd_small(cuda, native_lib, chunk, G):
+    from neptune_mlir import programs, runtime
+
+    B, L, H, P, N = 2, 512, 4, 64, 128
+    x, dt, A, Bm, Cm = inputs.ssd_inputs(B=B, L=L, H=H, P=P, N=N, G=G)
+    ws_bytes = runtime.ssd_workspace_bytes(B, L, H, P, N, G, chunk)
+    mod = translate_text(programs.ssd_chunk_scan_decl("ssd_small", B, L, H, P, N, G, chunk, ws_bytes), f"ssd_{chunk}_{G}")
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=cuda)
+    y = torch.full((B, L, H, P), float("nan"), dtype=torch.bfloat16, device=cuda)
+    mod.ssd_small(x.to(cuda), dt.to(cuda), A.to(cuda), Bm.to(cuda), Cm.to(cuda), ws, y)
+    finish()
+    ref = ssd.ssd_reference(x, dt, A, Bm, Cm)
+    # products of 128 bf16 terms are rounded once more to bf16 inside the kernel: 2 ulp relative
+    assert_storage_close(y, ref, 2 * BF16_ATOL, 2 * BF16_ULP)
+
+
+def test_ssd_config5_full_size_sampled(cuda, native_lib):
+    """B=4, L=8192, H=64, P=64, N=128, chunk 256; heads are independent, a sample is checked in full."""
+    from neptune_mlir import runtime
+
+    B, L, H, P, N, G, chunk = 4, 8192, 64, 64, 128, 1, 256
+    x, dt, A, Bm, Cm = (a.to(cuda) for a in inputs.ssd_inputs(B=B, L=L, H=H, P=P, N=N, G=G))
+    mod = translate_data("ssd_chunk_scan_bf16_4x8192x64x64")
+    ws = torch.empty(runtime.ssd_workspace_bytes(B, L, H, P, N, G, chunk), dtype=torch.uint8, device=cuda)
+    y = torch.full((B, L, H, P), float("nan"), dtype=torch.bfloat16, device=cuda)
+    mod.ssd_chunk_scan_bf16(x, dt, A, Bm, Cm, ws, y)
+    finish()
+    assert bool(torch.isfinite(y).all())
+    heads = [0, 63]
+    ref = ssd.ssd_reference(x[:1, :, heads].cpu(), dt[:1, :, heads].cpu(), A[heads].cpu(), Bm[:1].cpu(), Cm[:1].cpu())
+    assert_storage_close(y[:1, :, heads], ref, 2 * BF16_ATOL, 2 * BF16_ULP)
