@@ -38,8 +38,15 @@ def ssd_reference(x, dt, A, Bm, Cm):
     return y
 
 
-def ssd_chunked(x, dt, A, Bm, Cm, chunk: int):
+def ssd_chunked(x, dt, A, Bm, Cm, chunk: int, round_to=None):
     """Chunked form: intra-chunk masked products + fp32 state passed between chunks.
+
+    With ``round_to`` (a 16-bit dtype) the three places where the kernel feeds a computed fp32 value
+    back into a tensor-core product are rounded to that dtype, as the kernel must: the masked decayed
+    C.B^T block, the decay-weighted x of the chunk state, and the state entering a chunk (the fp32
+    master copy of the state is still what is carried).  This "kernel-faithful" form separates the
+    kernel's own arithmetic from the unavoidable operand rounding when outputs reach magnitudes of
+    several hundred.
 
     Per chunk with cum_i = sum_{s<=i} dt_s*A:
       Y_intra[i] = sum_{j<=i} (C_i.B_j) e^(cum_i-cum_j) dt_j x_j
@@ -60,16 +67,21 @@ def ssd_chunked(x, dt, A, Bm, Cm, chunk: int):
     y = torch.empty((Bsz, nc, chunk, H, P), dtype=torch.float32)
     S = torch.zeros((Bsz, H, P, N), dtype=torch.float32)
     tri = torch.tril(torch.ones(chunk, chunk, dtype=torch.bool))
+
+    def rnd(t):
+        return t if round_to is None else t.to(round_to).float()
+
     for c in range(nc):
         cb = torch.einsum("bihn,bjhn->bhij", Cf[:, c], Bf[:, c])           # [B, H, Q, Q]
         ci = cum[:, c].permute(0, 2, 1)                                   # [B, H, Q]
         decay = torch.exp((ci[:, :, :, None] - ci[:, :, None, :]).masked_fill(~tri, float("-inf")))
         w = cb * decay * dtc[:, c].permute(0, 2, 1)[:, :, None, :]
-        y_intra = torch.einsum("bhij,bjhp->bihp", w, xf[:, c])
-        y_inter = torch.einsum("bhpn,bihn->bihp", S, Cf[:, c]) * torch.exp(ci).permute(0, 2, 1)[..., None]
+        y_intra = torch.einsum("bhij,bjhp->bihp", rnd(w), xf[:, c])
+        y_inter = torch.einsum("bhpn,bihn->bihp", rnd(S), Cf[:, c]) * torch.exp(ci).permute(0, 2, 1)[..., None]
         y[:, c] = y_intra + y_inter
         last = ci[:, :, -1]                                               # [B, H]
         wz = torch.exp(last[:, :, None] - ci) * dtc[:, c].permute(0, 2, 1)  # [B, H, Q]
-        Z = torch.einsum("bhj,bjhp,bjhn->bhpn", wz, xf[:, c], Bf[:, c])
+        xs = rnd(wz.permute(0, 2, 1)[..., None] * xf[:, c])                 # [B, Q, H, P]
+        Z = torch.einsum("bjhp,bjhn->bhpn", xs, Bf[:, c])
         S = torch.exp(last)[:, :, None, None] * S + Z
     return y.view(Bsz, L, H, P)

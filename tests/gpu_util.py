@@ -48,18 +48,33 @@ def finish(device=None):
     runtime.check_status(device)
 
 
-def assert_storage_close(out: torch.Tensor, ref: torch.Tensor, atol: float, rel_ulp: float = 0.0):
-    """|out - ref| <= atol + rel_ulp*|ref| element-wise, on CPU in fp32.
+def assert_storage_close(out: torch.Tensor, ref: torch.Tensor, atol: float, rel_ulp: float = 0.0,
+                         scale_by_rms: bool = False):
+    """|out - ref| <= atol*scale + rel_ulp*|ref| element-wise, on CPU in fp32.
 
-    ``rel_ulp`` is used only for the scans, whose outputs reach magnitudes where one unit in the
-    last place of a 16-bit float exceeds the absolute tolerance (a bf16 ulp at 32 is 0.25), so that
-    even the correctly rounded result misses a purely absolute bound.
+    Attention and decode outputs are convex combinations of N(0,1) values, so scale = 1 and
+    rel_ulp = 0: a plain max-abs-error bound.  The scans' outputs are not bounded like that (the
+    SSD configuration reaches |y| of several hundred with an rms around 12), where one unit in the
+    last place of a 16-bit float already exceeds the absolute tolerance (a bf16 ulp at 256 is 2.0)
+    and where rounding a tensor-core operand to 16 bits moves a sum of cancelling terms by a fraction
+    of the terms' size, not of the sum's.  For them ``scale_by_rms`` scales the absolute part by
+    max(1, rms(ref)) and ``rel_ulp`` adds units in the last place of the reference value.
     """
     out = out.detach().float().cpu()
     ref = ref.detach().float().cpu()
     assert out.shape == ref.shape
     assert bool(torch.isfinite(out).all()), "output has non-finite values"
     err = (out - ref).abs()
-    bound = atol + rel_ulp * ref.abs()
+    scale = max(1.0, ref.pow(2).mean().sqrt().item()) if scale_by_rms else 1.0
+    bound = atol * scale + rel_ulp * ref.abs()
     worst = (err - bound).max().item()
     assert worst <= 0, f"max abs err {err.max().item():.3e}; worst excess over bound {worst:.3e}"
+
+
+def assert_rms_close(out: torch.Tensor, ref: torch.Tensor, rel: float):
+    """rms(out - ref) <= rel * rms(ref): catches systematic errors that a max-abs bound scaled for outliers would pass."""
+    out = out.detach().float().cpu()
+    ref = ref.detach().float().cpu()
+    err = (out - ref).pow(2).mean().sqrt().item()
+    scale = ref.pow(2).mean().sqrt().item()
+    assert err <= rel * scale, f"rms err {err:.3e} vs rms(ref) {scale:.3e}"
