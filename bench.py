@@ -227,7 +227,7 @@ def bench_attention(args, d: Dist, dev, flush, pk, pk_kind) -> dict:
     from neptune_mlir.sharding import shard_range
 
     S, D = ATTN["S"], ATTN["D"]
-    total_units = ATTN["B"] * ATTN["H"]
+    total_units = args.attn_units or ATTN["B"] * ATTN["H"]
     lo, hi = shard_range(total_units, d.rank, d.world)
     units = hi - lo
     fn = load_callable(programs.attention_htile("attention_prefill", units, 1, S, D, "bf16", causal=True), "attention_prefill")
@@ -249,6 +249,11 @@ def bench_attention(args, d: Dist, dev, flush, pk, pk_kind) -> dict:
                      "traffic": ATTN_DRAM_TRAFFIC_BYTES, "peak_source": f"of {pk_kind} (burst cuBLAS bf16)",
                      "kernel": "attn_fwd_tcgen05_kernel<bf16>"},
     }
+
+    result["gpu_launches"] = args.steps
+    if args.skip_e2e:
+        result["e2e"] = None
+        return result
 
     # ---- end to end: pinned host buffers, copies inside the timed region, chunked so that copies overlap compute
     chunk_units = max(1, units // 8)
@@ -292,7 +297,6 @@ def bench_attention(args, d: Dist, dev, flush, pk, pk_kind) -> dict:
                      "ms_per_step": ms_e2e, "steps": e2e_steps,
                      "how": f"{n_chunks} chunks of {chunk_units} units through the emitted function; H2D, kernel and "
                             "D2H on three streams from/to pinned host memory"}
-    result["gpu_launches"] = args.steps
     del q, k, v, out, dq, dk, dv, dout
     torch.cuda.empty_cache()
     return result
@@ -421,6 +425,10 @@ def main() -> None:
     ap.add_argument("--impl", choices=("native", "reference"), default="native")
     ap.add_argument("--skip-extra", action="store_true", help="attention only (skip decode and the scans)")
     ap.add_argument("--skip-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
+    ap.add_argument("--attn-units", type=int, default=0,
+                    help="number of (batch, head) units of the attention workload (default: the full 256); "
+                         "a reduced count is for profiler captures only and is recorded in config")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "native" else args.warmup
 
@@ -455,7 +463,8 @@ def main() -> None:
             "metric": "attn_prefill_tflops", "value": attn["value"], "unit": "TFLOP/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": attn["ms"], "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": attn_config(args.gpus), "roofline": attn["roofline"], "cpu_baseline": cpu, "e2e": attn["e2e"],
+            "config": attn_config(args.gpus) | ({"reduced_units": args.attn_units} if args.attn_units else {}),
+            "roofline": attn["roofline"], "cpu_baseline": cpu, "e2e": attn["e2e"],
             "gpu_launches": attn["gpu_launches"], "clocks": attn["clocks"], "workloads": extra,
         }
         print(json.dumps(line))

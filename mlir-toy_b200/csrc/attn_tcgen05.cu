@@ -344,6 +344,9 @@ int launch_tc(const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &t
   // per-device attribute: set on every call so that any current device is covered
   NB200_CHECK_CUDA(cudaFuncSetAttribute(attn_fwd_tcgen05_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         kSmemBytes));
+  // two CTAs of ~98 KB must fit: ask for the largest shared-memory carve-out
+  NB200_CHECK_CUDA(cudaFuncSetAttribute(attn_fwd_tcgen05_kernel<DT>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                        cudaSharedmemCarveoutMaxShared));
   const int n_qtiles = Sq / kBM;
   attn_fwd_tcgen05_kernel<DT><<<dim3(BH * n_qtiles), dim3(kThreads), kSmemBytes, st>>>(
       tq, tk, tv, static_cast<uint16_t *>(out), Sq, Skv, n_qtiles, scale_log2, causal, status);
