@@ -4,7 +4,8 @@
  * Every entry point takes raw device pointers, explicit extents, a dtype code and a CUDA stream
  * (a cudaStream_t passed as void*).  Calls are asynchronous on that stream and never synchronise
  * the device.  Nothing is allocated behind the caller's back: scratch memory is caller-provided
- * and sized by the matching *_workspace_bytes function.  Every function that can fail returns an
+ * and sized by the matching *_workspace_bytes function (nb200_decode_fwd_static, which uses a fixed
+ * array built into the library, is the one exception).  Every function that can fail returns an
  * int: 0 on success, a negative NB200_ERR_* code otherwise, with a thread-local message available
  * from nb200_last_error().  The library is safe to call from one host thread per GPU.
  *
@@ -95,6 +96,34 @@ int nb200_decode_splitk(const void *q, const void *k, const void *v, float *part
  */
 int nb200_decode_combine(const float *partials, void *out, int rows, int D, int n_splits,
                          long long row_stride, long long split_stride, int out_dtype, void *stream);
+
+/*
+ * Split-K decode plus combine for callers that may not allocate (no counterpart in the reference).
+ *
+ * Who needs it: a decode step issued from a serving loop whose memory plan was fixed at start-up.
+ * Such a host has handed whatever HBM was left to its KV cache, so a cudaMalloc for the partials can
+ * simply fail, and it must not call cudaMalloc / cudaFree in steady state anyway because both
+ * synchronise the whole device and stall every other stream of the server; a plugin embedded in a
+ * framework that owns the device allocator is in the same position.  This entry point therefore
+ * takes only inputs and the output: the per-split partials go to a fixed scratch array compiled
+ * into the library (NB200_DECODE_STATIC_SCRATCH_BYTES, resident on every GPU that loads the library
+ * until the process exits).  It calls no cudaMalloc, cudaFree or any other allocating routine.
+ *
+ *   arguments as nb200_decode_splitk, with `out` [B, Hq, D] in `dtype` as nb200_decode_combine writes it
+ *   limit: B * Hq * n_splits * (D + 2) * 4 bytes <= NB200_DECODE_STATIC_SCRATCH_BYTES, otherwise
+ *          NB200_ERR_UNSUPPORTED with a message naming both sizes (use the workspace entry points then)
+ *
+ * The first call on a device looks up the scratch array's device address (cudaGetSymbolAddress,
+ * once per device, with that device current); make that first call during start-up, before any
+ * stream capture begins.  All calls on a device share the one array, which keeps whatever the last
+ * call left in it; nothing needs clearing because every slot that is read is written first, but two
+ * calls whose kernels can overlap on the GPU (different streams, no dependency) race on it.
+ */
+#define NB200_DECODE_STATIC_SCRATCH_BYTES (4u << 20)
+
+int nb200_decode_fwd_static(const void *q, const void *k, const void *v, void *out,
+                            int B, int Hq, int Hkv, int Lkv, int D, int n_splits, int dtype,
+                            float scale_log2, void *stream);
 
 /*
  * Mamba-1 selective scan forward (no counterpart in the reference).

@@ -12,6 +12,8 @@
 //   * all arithmetic is fp32 (packed f32x2 FMAs), scores in the exp2 domain.
 // Per (row, split) the kernel writes the un-normalised output, the running maximum and the sum,
 // which nb200_decode_combine merges.
+#include <mutex>
+
 #include "nb200_common.cuh"
 
 namespace nb200 {
@@ -370,4 +372,57 @@ extern "C" int nb200_decode_combine(const float *partials, void *out, int rows, 
   }
   NB200_CHECK_CUDA(cudaGetLastError());
   return NB200_OK;
+}
+
+// ---- decode without any allocation ---------------------------------------------------------------
+// Scratch for nb200_decode_fwd_static: the split-K partials live in this fixed array instead of a
+// caller-provided workspace.  Every GPU on which the library is loaded carries these 4 MiB until
+// the process exits.  In host code the array's name only stands for the symbol; the address that a
+// kernel can use comes from cudaGetSymbolAddress, looked up once per device below.
+static __device__ __align__(256) unsigned char nb200_decode_static_scratch[NB200_DECODE_STATIC_SCRATCH_BYTES];
+
+namespace {
+
+constexpr int kMaxDevices = 64;
+std::mutex g_static_scratch_mutex;
+float *g_static_scratch_ptr[kMaxDevices] = {};
+
+// Device address of the scratch array on the current device (resolved on first use per device).
+int static_scratch_address(float **out) {
+  int dev = -1;
+  NB200_CHECK_CUDA(cudaGetDevice(&dev));
+  NB200_REQUIRE(dev >= 0 && dev < kMaxDevices, NB200_ERR_UNSUPPORTED, "decode_fwd_static: device index %d", dev);
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (g_static_scratch_ptr[dev] == nullptr) {
+    void *p = nullptr;
+    NB200_CHECK_CUDA(cudaGetSymbolAddress(&p, nb200_decode_static_scratch));
+    NB200_REQUIRE(p != nullptr, NB200_ERR_LAUNCH, "decode_fwd_static: cudaGetSymbolAddress returned null");
+    g_static_scratch_ptr[dev] = static_cast<float *>(p);
+  }
+  *out = g_static_scratch_ptr[dev];
+  return NB200_OK;
+}
+
+}  // namespace
+
+extern "C" int nb200_decode_fwd_static(const void *q, const void *k, const void *v, void *out, int B, int Hq,
+                                       int Hkv, int Lkv, int D, int n_splits, int dtype, float scale_log2,
+                                       void *stream) {
+  NB200_REQUIRE(q && k && v && out, NB200_ERR_BAD_ARG, "decode_fwd_static: null pointer");
+  NB200_REQUIRE(B > 0 && Hq > 0 && Hkv > 0 && Lkv > 0 && D > 0 && n_splits > 0, NB200_ERR_BAD_ARG,
+                "decode_fwd_static: non-positive extent");
+  const size_t need = (size_t)B * Hq * n_splits * ((size_t)D + 2) * sizeof(float);
+  NB200_REQUIRE(need <= (size_t)NB200_DECODE_STATIC_SCRATCH_BYTES, NB200_ERR_UNSUPPORTED,
+                "decode_fwd_static: B*Hq*n_splits*(D+2) floats = %zu bytes of partials do not fit the built-in "
+                "%zu-byte scratch; call nb200_decode_splitk / nb200_decode_combine with your own workspace",
+                need, (size_t)NB200_DECODE_STATIC_SCRATCH_BYTES);
+  float *partials = nullptr;
+  const int rc = static_scratch_address(&partials);
+  if (rc != NB200_OK) return rc;
+  // Split-K writes every (row, split) slot that the combine reads, so nothing left in the array by
+  // an earlier call can leak into this one and nothing has to be cleared first.
+  const int rc1 = nb200_decode_splitk(q, k, v, partials, B, Hq, Hkv, Lkv, D, n_splits, dtype, scale_log2, stream);
+  if (rc1 != NB200_OK) return rc1;
+  return nb200_decode_combine(partials, out, B * Hq, D, n_splits, (long long)n_splits * (D + 2), D + 2, dtype,
+                              stream);
 }
