@@ -11,7 +11,8 @@
 //                       TMEM (it overwrites S in place as packed 16-bit) and V as an MN-major
 //                       smem operand, accumulator in TMEM columns 128..255
 //   warps 0-3           softmax: thread r owns row r (TMEM lane r), so row max and row sum need
-//                       no cross-thread traffic; two passes over S (max, then exp2 / sum / pack);
+//                       no cross-thread traffic; the row is read from TMEM once into registers
+//                       (three-input maxima, packed f32x2 scale/sum, exp2, pack to 16 bit);
 //                       O is rescaled in TMEM only when a row maximum grows by more than 2^8,
 //                       which leaves the result unchanged (the same stale maximum scales P and
 //                       the running sum) but makes the rescale rare
@@ -206,19 +207,25 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
       tc_fence_after();
       const bool diag = (j == jdiag);
 
-      // ---- pass 1: row maximum of this block ----
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < kBN / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld32(tS + lane_addr + c * 32, v);
-        tmem_wait_ld();
+      // ---- the whole row of S into registers (one TMEM read), masked on the diagonal block ----
+      uint32_t v[kBN];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float s = __uint_as_float(v[i]);
-          mx = (diag && (c * 32 + i > r)) ? mx : fmaxf(mx, s);
-        }
+      for (int c = 0; c < kBN / 32; ++c) tmem_ld32p(tS + lane_addr + c * 32, v + c * 32);
+      tmem_wait_ld();
+      if (diag) {
+#pragma unroll
+        for (int i = 0; i < kBN; ++i) v[i] = (i > r) ? 0xff800000u : v[i];  // -inf: 2^(-inf) = 0
       }
+
+      // ---- row maximum (two independent chains of three-input maxima) ----
+      float mxa = max3(__uint_as_float(v[0]), __uint_as_float(v[1]), __uint_as_float(v[2]));
+      float mxb = max3(__uint_as_float(v[3]), __uint_as_float(v[4]), __uint_as_float(v[5]));
+#pragma unroll
+      for (int i = 6; i + 3 < kBN; i += 4) {
+        mxa = max3(mxa, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+        mxb = max3(mxb, __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+      }
+      const float mx = max3(mxa, mxb, fmaxf(__uint_as_float(v[kBN - 2]), __uint_as_float(v[kBN - 1])));
       const float m_blk = mx * scale_log2;                   // scale_log2 > 0
       if (j == 0) {
         m_used = m_blk;
@@ -231,37 +238,36 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
           // PV(j-1) has retired: the commit that signalled s_full(j) was issued after it.
 #pragma unroll 1
           for (int c = 0; c < kD / 32; ++c) {
-            uint32_t v[32];
-            tmem_ld32(tO + lane_addr + c * 32, v);
+            uint32_t o[32];
+            tmem_ld32(tO + lane_addr + c * 32, o);
             tmem_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
-            tmem_st32(tO + lane_addr + c * 32, v);
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+            tmem_st32(tO + lane_addr + c * 32, o);
           }
           tmem_wait_st();
         }
       }
 
-      // ---- pass 2: p = 2^(s*scale - m), row sum, pack to 16 bit, write P over S ----
-      const float neg_m = -m_used;
-#pragma unroll 1
+      // ---- p = 2^(s*scale - m) on packed pairs, row sum, pack to 16 bit, write P over S ----
+      const uint64_t c2 = f2_pack(scale_log2, scale_log2), nm2 = f2_pack(-m_used, -m_used);
+      uint64_t lsum2 = f2_pack(0.f, 0.f);
+#pragma unroll
       for (int c = 0; c < kBN / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld32(tS + lane_addr + c * 32, v);
-        tmem_wait_ld();
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          float p0 = ex2(fmaf(__uint_as_float(v[2 * i]), scale_log2, neg_m));
-          float p1 = ex2(fmaf(__uint_as_float(v[2 * i + 1]), scale_log2, neg_m));
-          if (diag) {
-            p0 = (c * 32 + 2 * i > r) ? 0.f : p0;
-            p1 = (c * 32 + 2 * i + 1 > r) ? 0.f : p1;
-          }
-          l += p0 + p1;
+          const float2 x = f2_unpack(f2_fma(
+              f2_pack(__uint_as_float(v[c * 32 + 2 * i]), __uint_as_float(v[c * 32 + 2 * i + 1])), c2, nm2));
+          const float p0 = ex2(x.x), p1 = ex2(x.y);
+          lsum2 = f2_add(lsum2, f2_pack(p0, p1));
           pk[i] = pack2<DT>(p0, p1);
         }
         tmem_st16(tS + lane_addr + c * 16, pk);
+      }
+      {
+        const float2 ls = f2_unpack(lsum2);
+        l += ls.x + ls.y;
       }
       tmem_wait_st();
       tc_fence_before();

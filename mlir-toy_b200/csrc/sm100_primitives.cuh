@@ -48,24 +48,37 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// try_wait that lets the hardware suspend the thread for up to `hint_ns` while the phase is pending,
+// so that a waiting warp does not compete for issue slots with the warps doing the arithmetic.
+__device__ __forceinline__ bool mbar_try_wait_suspend(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+
 // Wait for a phase with a wall-clock limit.  Returns false if the limit passed or if another
 // thread of the CTA has already given up (abort_flag set); the caller then unwinds to the common
 // tear-down instead of spinning forever.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
-#pragma unroll 1
-  for (int i = 0; i < 2048; ++i)
-    if (mbar_try_wait(bar, parity)) return true;
+  if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
 #pragma unroll 1
   while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait_suspend(bar, parity, 200000u)) return true;  // wakes as soon as the phase completes
     if (*abort_flag) return false;
     if (globaltimer_ns() - t0 > kWaitLimitNs) {
       *abort_flag = 1;
       return false;
     }
-    __nanosleep(64);
   }
 }
 
@@ -106,6 +119,19 @@ __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.
 // Warp-collective: lane i of the warp reads 32 consecutive 32-bit columns of TMEM lane
 // (taddr.lane + i).  A warp may only touch the 32 lanes of its own quarter (warp index mod 4).
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+// Same, into 32 consecutive elements of a larger register array.
+__device__ __forceinline__ void tmem_ld32p(uint32_t taddr, uint32_t *r) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
       "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
