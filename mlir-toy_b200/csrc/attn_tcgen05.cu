@@ -4,15 +4,19 @@
 // of 128 rows, with the online softmax of the HTile program
 // (tests/data/flash_attention_htile.mlir:40-143 of the reference) kept in the exp2 domain:
 //
-//   warp 4 (one lane)   TMA producer: Q once, then K(j), V(j) into single 32 KB buffers each,
+//   warp 8 (one lane)   TMA producer: Q once, then K(j), V(j) into single 32 KB buffers each,
 //                       128-byte swizzled, re-armed as soon as the MMA that read them has retired
-//   warp 5 (one lane)   MMA issuer: S = Q K(j)^T (8 x tcgen05.mma 128x128x16, operands in smem,
+//   warp 9 (one lane)   MMA issuer: S = Q K(j)^T (8 x tcgen05.mma 128x128x16, operands in smem,
 //                       accumulator in TMEM columns 0..127), then O += P V(j) with P read from
 //                       TMEM (it overwrites S in place as packed 16-bit) and V as an MN-major
 //                       smem operand, accumulator in TMEM columns 128..255
-//   warps 0-3           softmax: thread r owns row r (TMEM lane r), so row max and row sum need
-//                       no cross-thread traffic; the row is read from TMEM once into registers
-//                       (three-input maxima, packed f32x2 scale/sum, exp2, pack to 16 bit);
+//   warps 0-7           softmax: a row lives in one TMEM lane, and a TMEM lane quarter can only be
+//                       read by warps whose index mod 4 names it, so warps q and q+4 share the 32
+//                       rows of quarter q and each takes 64 of the 128 columns: a single warp
+//                       issuing a whole row's ~640 instructions was the longest link of the
+//                       per-block dependency chain.  The half row is read from TMEM once into
+//                       registers (three-input maxima, packed f32x2 scale/sum, exp2, pack to
+//                       16 bit); the two half-row maxima are exchanged through shared memory.
 //                       O is rescaled in TMEM only when a row maximum grows by more than 2^8,
 //                       which leaves the result unchanged (the same stale maximum scales P and
 //                       the running sum) but makes the rescale rare
@@ -22,6 +26,8 @@
 // heads (K/V stay in L2) and, for causal problems, the long tiles of a head are issued first.
 // Every wait is bounded; on expiry the CTA records a code in the status words and unwinds.
 #include <cuda.h>
+
+#include <cstdlib>
 
 #include "nb200_common.cuh"
 #include "sm100_primitives.cuh"
@@ -34,20 +40,25 @@ using namespace sm100;
 constexpr int kBM = 128;            // query rows per CTA
 constexpr int kBN = 128;            // kv rows per step
 constexpr int kD = 128;             // head dimension
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;
+constexpr int kSoftmaxThreads = 256;
+constexpr int kProducerWarp = 8, kMmaWarp = 9;
 constexpr int kTileBytes = kBM * kD * 2;        // 32 KB: two 64-column boxes of 16 KB
 constexpr int kBoxBytes = kTileBytes / 2;
 constexpr int kTmemCols = 256;
-constexpr int kSmemBytes = 3 * kTileBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int kSmemBytes = 3 * kTileBytes + 1024 /*alignment slack*/ + 4096 /*barriers + exchange*/;
 constexpr float kRescaleThreshold = 8.0f;       // log2 units
 
 enum : int { kErrProducer = 1, kErrMma = 2, kErrSoftmax = 3, kErrEpilogue = 4 };
 
 struct Barriers {
   uint64_t q_full, k_full, k_empty, v_full, v_empty, s_full, p_full, o_full;
+  uint64_t pair[4];          // one per lane quarter: the two warps that share its rows meet here
   uint32_t tmem_base;
   int abort_flag;
   int skip;
+  float xmax[2][2][kBM];     // [block parity][column half][row]: half-row maxima
+  float xsum[2][kBM];        // [column half][row]: half-row sums, exchanged once at the end
 };
 
 __device__ __forceinline__ void report(int *status, int code, int detail) {
@@ -58,7 +69,28 @@ __device__ __forceinline__ void report(int *status, int code, int detail) {
   }
 }
 
-template <int DT>
+// 2^x for a packed pair on the FMA pipe: round-to-nearest split x = n + f with the 1.5*2^23 trick,
+// degree-3 minimax polynomial for 2^f on [-0.5, 0.5] (max relative error 7.5e-5, far below the
+// rounding of P to 16 bits), exponent added to the bits.  x is clamped at -126 (result ~1e-38).
+__device__ __forceinline__ float2 ex2_poly_pair(uint64_t x2) {
+  float2 x = f2_unpack(x2);
+  x.x = fmaxf(x.x, -126.f);
+  x.y = fmaxf(x.y, -126.f);
+  const uint64_t xc = f2_pack(x.x, x.y);
+  const uint64_t magic = f2_pack(12582912.f, 12582912.f), neg_magic = f2_pack(-12582912.f, -12582912.f);
+  const uint64_t t2 = f2_add(xc, magic);                                  // low mantissa bits = round(x)
+  const uint64_t f2 = f2_fma(f2_add(t2, neg_magic), f2_pack(-1.f, -1.f), xc);  // x - round(x)
+  uint64_t r2 = f2_fma(f2, f2_pack(0.05517164617776871f, 0.05517164617776871f),
+                       f2_pack(0.2426111251115799f, 0.2426111251115799f));
+  r2 = f2_fma(r2, f2, f2_pack(0.6932609677314758f, 0.6932609677314758f));
+  r2 = f2_fma(r2, f2, f2_pack(0.9999280571937561f, 0.9999280571937561f));
+  const float2 r = f2_unpack(r2), t = f2_unpack(t2);
+  return make_float2(__int_as_float(__float_as_int(r.x) + (__float_as_int(t.x) << 23)),
+                     __int_as_float(__float_as_int(r.y) + (__float_as_int(t.y) << 23)));
+}
+
+// POLY = how many of every 8 pairs take their exponential on the FMA pipe instead of the MUFU.
+template <int DT, int POLY>
 __global__ void __launch_bounds__(kThreads, 2)
 attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                         const __grid_constant__ CUtensorMap tm_v, uint16_t *__restrict__ out, int Sq, int Skv,
@@ -91,7 +123,8 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
     mbar_init(smem_u32(&bars->v_full), 1);
     mbar_init(smem_u32(&bars->v_empty), 1);
     mbar_init(smem_u32(&bars->s_full), 1);
-    mbar_init(smem_u32(&bars->p_full), 128);
+    mbar_init(smem_u32(&bars->p_full), kSoftmaxThreads);
+    for (int q4 = 0; q4 < 4; ++q4) mbar_init(smem_u32(&bars->pair[q4]), 64);
     mbar_init(smem_u32(&bars->o_full), 1);
     fence_barrier_init();
     fence_proxy_async_smem();
@@ -99,11 +132,11 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
   __syncthreads();
   if (bars->skip) return;  // an earlier CTA of this launch already reported a failure
 
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     tmem_alloc(smem_u32(&bars->tmem_base), kTmemCols);
     tmem_relinquish();
   }
-  if (warp == 4 && lane == 0) {
+  if (warp == kProducerWarp && lane == 0) {
     tma_prefetch_desc(&tm_q);
     tma_prefetch_desc(&tm_k);
     tma_prefetch_desc(&tm_v);
@@ -119,7 +152,7 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                  b_v_empty = smem_u32(&bars->v_empty), b_s_full = smem_u32(&bars->s_full),
                  b_p_full = smem_u32(&bars->p_full), b_o_full = smem_u32(&bars->o_full);
 
-  if (warp == 4) {
+  if (warp == kProducerWarp) {
     // ================================ TMA producer ================================
     if (lane == 0) {
       mbar_arrive_expect_tx(b_q_full, kTileBytes);
@@ -154,7 +187,7 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
       }
     }
     __syncwarp();
-  } else if (warp == 5) {
+  } else if (warp == kMmaWarp) {
     // ================================ MMA issuer ==================================
     if (lane == 0) {
       constexpr int fmt = (DT == NB200_BF16) ? 1 : 0;
@@ -177,10 +210,11 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         umma_commit(b_k_empty);
         umma_commit(b_s_full);
 
-        ok = mbar_wait(b_p_full, ph, abort_flag);
-        if (!ok) { report(status, kErrMma, 3 * j + 1); break; }
+        // V(j) normally landed long ago; take that wait off the path that follows the softmax
         ok = mbar_wait(b_v_full, ph, abort_flag);
         if (!ok) { report(status, kErrMma, 3 * j + 2); break; }
+        ok = mbar_wait(b_p_full, ph, abort_flag);
+        if (!ok) { report(status, kErrMma, 3 * j + 1); break; }
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < kBN / 16; ++kk) {
@@ -195,8 +229,11 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
     __syncwarp();
   } else {
     // ================================ softmax + epilogue ==========================
-    const int r = warp * 32 + lane;                         // row in the tile == TMEM lane
-    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    const int q4 = warp & 3, half = warp >> 2;              // lane quarter, column half
+    const int r = q4 * 32 + lane;                           // row in the tile == TMEM lane
+    const uint32_t lane_addr = static_cast<uint32_t>(q4 * 32) << 16;
+    const int col0 = half * (kBN / 2);                      // this thread's 64 columns of S and of O
+    const uint32_t b_pair = smem_u32(&bars->pair[q4]);
     const int jdiag = causal ? (nblk - 1) : -1;
     float m_used = -INFINITY, l = 0.f;
     bool ok = true;
@@ -207,43 +244,55 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
       tc_fence_after();
       const bool diag = (j == jdiag);
 
-      // ---- the whole row of S into registers (one TMEM read), masked on the diagonal block ----
-      uint32_t v[kBN];
-#pragma unroll
-      for (int c = 0; c < kBN / 32; ++c) tmem_ld32p(tS + lane_addr + c * 32, v + c * 32);
+      // ---- this thread's half row of S into registers (one TMEM read), masked on the diagonal block ----
+      uint32_t v[kBN / 2];
+      tmem_ld32p(tS + lane_addr + col0, v);
+      tmem_ld32p(tS + lane_addr + col0 + 32, v + 32);
       tmem_wait_ld();
       if (diag) {
 #pragma unroll
-        for (int i = 0; i < kBN; ++i) v[i] = (i > r) ? 0xff800000u : v[i];  // -inf: 2^(-inf) = 0
+        for (int i = 0; i < kBN / 2; ++i) v[i] = (col0 + i > r) ? 0xff800000u : v[i];  // -inf: 2^(-inf) = 0
       }
 
-      // ---- row maximum (two independent chains of three-input maxima) ----
-      float mxa = max3(__uint_as_float(v[0]), __uint_as_float(v[1]), __uint_as_float(v[2]));
-      float mxb = max3(__uint_as_float(v[3]), __uint_as_float(v[4]), __uint_as_float(v[5]));
+      // ---- half-row maximum (four chains of three-input maxima), then the partner's half ----
+      float mc[4];
 #pragma unroll
-      for (int i = 6; i + 3 < kBN; i += 4) {
-        mxa = max3(mxa, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
-        mxb = max3(mxb, __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+      for (int c = 0; c < 4; ++c)
+        mc[c] = max3(__uint_as_float(v[c * 16]), __uint_as_float(v[c * 16 + 1]), __uint_as_float(v[c * 16 + 2]));
+#pragma unroll
+      for (int i = 3; i + 1 < 16; i += 2) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          mc[c] = max3(mc[c], __uint_as_float(v[c * 16 + i]), __uint_as_float(v[c * 16 + i + 1]));
       }
-      const float mx = max3(mxa, mxb, fmaxf(__uint_as_float(v[kBN - 2]), __uint_as_float(v[kBN - 1])));
+#pragma unroll
+      for (int c = 0; c < 4; ++c) mc[c] = fmaxf(mc[c], __uint_as_float(v[c * 16 + 15]));
+      float mx = fmaxf(max3(mc[0], mc[1], mc[2]), mc[3]);
+      bars->xmax[j & 1][half][r] = mx;
+      mbar_arrive(b_pair);
+      // Passing this barrier also means the partner has finished reading its columns of S, some of
+      // which this thread's P will overwrite.
+      ok = __all_sync(0xffffffffu, mbar_wait(b_pair, j & 1, abort_flag));
+      if (!ok) { report(status, kErrSoftmax, 1000 + j); break; }
+      mx = fmaxf(mx, bars->xmax[j & 1][half ^ 1][r]);
       const float m_blk = mx * scale_log2;                   // scale_log2 > 0
       if (j == 0) {
         m_used = m_blk;
       } else {
         const bool need = m_blk > m_used + kRescaleThreshold;
-        if (__any_sync(0xffffffffu, need)) {
+        if (__any_sync(0xffffffffu, need)) {                 // same rows, same values: both warps of a pair agree
           const float f = need ? ex2(m_used - m_blk) : 1.f;
           if (need) m_used = m_blk;
           l *= f;
           // PV(j-1) has retired: the commit that signalled s_full(j) was issued after it.
 #pragma unroll 1
-          for (int c = 0; c < kD / 32; ++c) {
-            uint32_t o[32];
-            tmem_ld32(tO + lane_addr + c * 32, o);
+          for (int c = 0; c < 4; ++c) {  // 16 columns at a time: the half row of S stays live in registers
+            uint32_t o[16];
+            tmem_ld16(tO + lane_addr + col0 + c * 16, o);
             tmem_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
-            tmem_st32(tO + lane_addr + c * 32, o);
+            for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+            tmem_st16(tO + lane_addr + col0 + c * 16, o);
           }
           tmem_wait_st();
         }
@@ -253,17 +302,26 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
       const uint64_t c2 = f2_pack(scale_log2, scale_log2), nm2 = f2_pack(-m_used, -m_used);
       uint64_t lsum2 = f2_pack(0.f, 0.f);
 #pragma unroll
-      for (int c = 0; c < kBN / 32; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          const float2 x = f2_unpack(f2_fma(
-              f2_pack(__uint_as_float(v[c * 32 + 2 * i]), __uint_as_float(v[c * 32 + 2 * i + 1])), c2, nm2));
-          const float p0 = ex2(x.x), p1 = ex2(x.y);
+          const uint64_t x2 = f2_fma(
+              f2_pack(__uint_as_float(v[c * 32 + 2 * i]), __uint_as_float(v[c * 32 + 2 * i + 1])), c2, nm2);
+          float p0, p1;
+          if ((i & 7) < POLY) {
+            const float2 pp = ex2_poly_pair(x2);
+            p0 = pp.x;
+            p1 = pp.y;
+          } else {
+            const float2 x = f2_unpack(x2);
+            p0 = ex2(x.x);
+            p1 = ex2(x.y);
+          }
           lsum2 = f2_add(lsum2, f2_pack(p0, p1));
           pk[i] = pack2<DT>(p0, p1);
         }
-        tmem_st16(tS + lane_addr + c * 16, pk);
+        tmem_st16(tS + lane_addr + col0 / 2 + c * 16, pk);   // 64 columns of S -> 32 packed columns of P
       }
       {
         const float2 ls = f2_unpack(lsum2);
@@ -274,27 +332,34 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
       mbar_arrive(b_p_full);
     }
 
-    // ---- epilogue: O / l -> storage dtype -> global ----
+    // ---- epilogue: O / l -> storage dtype -> global; each thread writes its 64 columns ----
     if (ok) {
+      bars->xsum[half][r] = l;
+      mbar_arrive(b_pair);
+      ok = __all_sync(0xffffffffu, mbar_wait(b_pair, nblk & 1, abort_flag));
+      if (!ok) report(status, kErrEpilogue, 1);
+    }
+    if (ok) {
+      l += bars->xsum[half ^ 1][r];
       ok = __all_sync(0xffffffffu, mbar_wait(b_o_full, 0, abort_flag));
       if (!ok) report(status, kErrEpilogue, 0);
     }
     if (ok) {
       tc_fence_after();
       const float inv = 1.f / l;
-      uint16_t *dst = out + (static_cast<size_t>(q_row0) + r) * kD;
+      uint16_t *dst = out + (static_cast<size_t>(q_row0) + r) * kD + col0;
 #pragma unroll 1
-      for (int c = 0; c < kD / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld32(tO + lane_addr + c * 32, v);
+      for (int c = 0; c < 2; ++c) {
+        uint32_t o[32];
+        tmem_ld32(tO + lane_addr + col0 + c * 32, o);
         tmem_wait_ld();
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           uint4 w;
-          w.x = pack2<DT>(__uint_as_float(v[8 * i + 0]) * inv, __uint_as_float(v[8 * i + 1]) * inv);
-          w.y = pack2<DT>(__uint_as_float(v[8 * i + 2]) * inv, __uint_as_float(v[8 * i + 3]) * inv);
-          w.z = pack2<DT>(__uint_as_float(v[8 * i + 4]) * inv, __uint_as_float(v[8 * i + 5]) * inv);
-          w.w = pack2<DT>(__uint_as_float(v[8 * i + 6]) * inv, __uint_as_float(v[8 * i + 7]) * inv);
+          w.x = pack2<DT>(__uint_as_float(o[8 * i + 0]) * inv, __uint_as_float(o[8 * i + 1]) * inv);
+          w.y = pack2<DT>(__uint_as_float(o[8 * i + 2]) * inv, __uint_as_float(o[8 * i + 3]) * inv);
+          w.z = pack2<DT>(__uint_as_float(o[8 * i + 4]) * inv, __uint_as_float(o[8 * i + 5]) * inv);
+          w.w = pack2<DT>(__uint_as_float(o[8 * i + 6]) * inv, __uint_as_float(o[8 * i + 7]) * inv);
           *reinterpret_cast<uint4 *>(dst + c * 32 + i * 8) = w;
         }
       }
@@ -304,7 +369,7 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
   // ================================ tear-down =====================================
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     tc_fence_after();
     tmem_dealloc(tmem, kTmemCols);
   }
@@ -344,17 +409,17 @@ int make_tile_map(CUtensorMap *tm, const void *ptr, long long rows, int dtype) {
   return NB200_OK;
 }
 
-template <int DT>
+template <int DT, int POLY>
 int launch_tc(const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv, void *out, int BH, int Sq,
               int Skv, float scale_log2, int causal, int *status, cudaStream_t st) {
   // per-device attribute: set on every call so that any current device is covered
-  NB200_CHECK_CUDA(cudaFuncSetAttribute(attn_fwd_tcgen05_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  NB200_CHECK_CUDA(cudaFuncSetAttribute(attn_fwd_tcgen05_kernel<DT, POLY>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         kSmemBytes));
   // two CTAs of ~98 KB must fit: ask for the largest shared-memory carve-out
-  NB200_CHECK_CUDA(cudaFuncSetAttribute(attn_fwd_tcgen05_kernel<DT>, cudaFuncAttributePreferredSharedMemoryCarveout,
+  NB200_CHECK_CUDA(cudaFuncSetAttribute(attn_fwd_tcgen05_kernel<DT, POLY>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                         cudaSharedmemCarveoutMaxShared));
   const int n_qtiles = Sq / kBM;
-  attn_fwd_tcgen05_kernel<DT><<<dim3(BH * n_qtiles), dim3(kThreads), kSmemBytes, st>>>(
+  attn_fwd_tcgen05_kernel<DT, POLY><<<dim3(BH * n_qtiles), dim3(kThreads), kSmemBytes, st>>>(
       tq, tk, tv, static_cast<uint16_t *>(out), Sq, Skv, n_qtiles, scale_log2, causal, status);
   NB200_CHECK_CUDA(cudaGetLastError());
   return NB200_OK;
@@ -391,7 +456,24 @@ extern "C" int nb200_attn_fwd(const void *q, const void *k, const void *v, void 
   if ((rc = make_tile_map(&tq, q, (long long)B * H * Sq, dtype)) != NB200_OK) return rc;
   if ((rc = make_tile_map(&tk, k, (long long)B * H * Skv, dtype)) != NB200_OK) return rc;
   if ((rc = make_tile_map(&tv, v, (long long)B * H * Skv, dtype)) != NB200_OK) return rc;
-  if (dtype == NB200_BF16)
-    return launch_tc<NB200_BF16>(tq, tk, tv, out, B * H, Sq, Skv, scale_log2, causal, status, st);
-  return launch_tc<NB200_F16>(tq, tk, tv, out, B * H, Sq, Skv, scale_log2, causal, status, st);
+  static const int poly = [] {
+    const char *e = getenv("NB200_ATTN_POLY");
+    return e ? atoi(e) : 0;
+  }();
+#define NB200_TC(DTV, PV) launch_tc<DTV, PV>(tq, tk, tv, out, B * H, Sq, Skv, scale_log2, causal, status, st)
+  if (dtype == NB200_BF16) {
+    switch (poly) {
+      case 2: return NB200_TC(NB200_BF16, 2);
+      case 3: return NB200_TC(NB200_BF16, 3);
+      case 4: return NB200_TC(NB200_BF16, 4);
+      default: return NB200_TC(NB200_BF16, 0);
+    }
+  }
+  switch (poly) {
+    case 2: return NB200_TC(NB200_F16, 2);
+    case 3: return NB200_TC(NB200_F16, 3);
+    case 4: return NB200_TC(NB200_F16, 4);
+    default: return NB200_TC(NB200_F16, 0);
+  }
+#undef NB200_TC
 }
