@@ -1,30 +1,30 @@
 // Fused attention forward on Blackwell tensor cores (f16 / bf16 storage, D = 128).
 //
 // One CTA computes a tile of 128 query rows of one (batch, head) against the KV sequence in blocks
-// of 128 rows, with the online softmax of the HTile program
-// (tests/data/flash_attention_htile.mlir:40-143 of the reference) kept in the exp2 domain:
+// of 64 rows, with the online softmax of the HTile program
+// (tests/data/flash_attention_htile.mlir:40-143 of the reference) kept in the exp2 domain.  The
+// three stages of a block -- S = Q K^T, softmax, O += P V -- form a software pipeline that is two
+// blocks deep, so the tensor pipe computes S(j+1) and S(j+2) while the softmax warps work on S(j):
 //
-//   warp 8 (one lane)   TMA producer: Q once, then K(j), V(j) into single 32 KB buffers each,
-//                       128-byte swizzled, re-armed as soon as the MMA that read them has retired
-//   warp 9 (one lane)   MMA issuer: S = Q K(j)^T (8 x tcgen05.mma 128x128x16, operands in smem,
-//                       accumulator in TMEM columns 0..127), then O += P V(j) with P read from
-//                       TMEM (it overwrites S in place as packed 16-bit) and V as an MN-major
-//                       smem operand, accumulator in TMEM columns 128..255
-//   warps 0-7           softmax: a row lives in one TMEM lane, and a TMEM lane quarter can only be
-//                       read by warps whose index mod 4 names it, so warps q and q+4 share the 32
-//                       rows of quarter q and each takes 64 of the 128 columns: a single warp
-//                       issuing a whole row's ~640 instructions was the longest link of the
-//                       per-block dependency chain.  The half row is read from TMEM once into
-//                       registers (three-input maxima, packed f32x2 scale/sum, exp2, pack to
-//                       16 bit); the two half-row maxima are exchanged through shared memory.
+//   warp 4 (one lane)   TMA producer: Q once, then K(j), V(j) into two 16 KB buffers each
+//                       (128-byte swizzled), re-armed when the MMA that read a buffer has retired
+//   warp 5 (one lane)   MMA issuer, operand descriptors built once: S_b = Q K(j)^T
+//                       (8 x tcgen05.mma 128x64x16, both operands in smem) into one of two
+//                       64-column TMEM buffers b = j mod 2, issued two blocks ahead;
+//                       O += P_b V(j) (4 x tcgen05.mma 128x128x16) with P read from TMEM, where it
+//                       overwrites S_b in place as packed 16-bit, and V as an MN-major smem
+//                       operand; the accumulator O lives in TMEM columns 128..255
+//   warps 0-3           softmax: thread r owns row r (TMEM lane r), so row max and row sum need no
+//                       cross-thread traffic; the 64 scores are read from TMEM once into registers
+//                       (three-input maxima, packed f32x2 scale/sum, exp2, pack to 16 bit).
 //                       O is rescaled in TMEM only when a row maximum grows by more than 2^8,
 //                       which leaves the result unchanged (the same stale maximum scales P and
 //                       the running sum) but makes the rescale rare
 //
-// Two CTAs are resident per SM (98 KB smem, 256 TMEM columns each), so one CTA's softmax overlaps
-// the other's MMAs.  Tiles are numbered so that CTAs running at the same time work on the same few
-// heads (K/V stay in L2) and, for causal problems, the long tiles of a head are issued first.
-// Every wait is bounded; on expiry the CTA records a code in the status words and unwinds.
+// Two CTAs are resident per SM (96 KB smem, 256 TMEM columns each).  Tiles are numbered so that
+// CTAs running at the same time work on the same few heads (K/V stay in L2) and, for causal
+// problems, the long tiles of a head are issued first.  Every wait is bounded; on expiry the CTA
+// records a code in the status words and unwinds.
 #include <cuda.h>
 
 #include <cstdlib>
@@ -38,27 +38,24 @@ namespace {
 using namespace sm100;
 
 constexpr int kBM = 128;            // query rows per CTA
-constexpr int kBN = 128;            // kv rows per step
+constexpr int kBN = 64;             // kv rows per pipeline step
 constexpr int kD = 128;             // head dimension
-constexpr int kThreads = 320;
-constexpr int kSoftmaxThreads = 256;
-constexpr int kProducerWarp = 8, kMmaWarp = 9;
-constexpr int kTileBytes = kBM * kD * 2;        // 32 KB: two 64-column boxes of 16 KB
-constexpr int kBoxBytes = kTileBytes / 2;
-constexpr int kTmemCols = 256;
-constexpr int kSmemBytes = 3 * kTileBytes + 1024 /*alignment slack*/ + 4096 /*barriers + exchange*/;
+constexpr int kThreads = 192;
+constexpr int kQBytes = kBM * kD * 2;           // 32 KB: two 64-column boxes of 16 KB
+constexpr int kQBox = kQBytes / 2;
+constexpr int kKVBytes = kBN * kD * 2;          // 16 KB: two 64-column boxes of 8 KB
+constexpr int kKVBox = kKVBytes / 2;
+constexpr int kTmemCols = 256;                  // S0 | S1 | O
+constexpr int kSmemBytes = kQBytes + 4 * kKVBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
 constexpr float kRescaleThreshold = 8.0f;       // log2 units
 
 enum : int { kErrProducer = 1, kErrMma = 2, kErrSoftmax = 3, kErrEpilogue = 4 };
 
 struct Barriers {
-  uint64_t q_full, k_full, k_empty, v_full, v_empty, s_full, p_full, o_full;
-  uint64_t pair[4];          // one per lane quarter: the two warps that share its rows meet here
+  uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full[2], pv_done, o_full;
   uint32_t tmem_base;
   int abort_flag;
   int skip;
-  float xmax[2][2][kBM];     // [block parity][column half][row]: half-row maxima
-  float xsum[2][kBM];        // [column half][row]: half-row sums, exchanged once at the end
 };
 
 __device__ __forceinline__ void report(int *status, int code, int detail) {
@@ -99,8 +96,9 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   unsigned char *smem = smem_raw + (base - raw);
-  const uint32_t sQ = base, sK = base + kTileBytes, sV = base + 2 * kTileBytes;
-  Barriers *bars = reinterpret_cast<Barriers *>(smem + 3 * kTileBytes);
+  const uint32_t sQ = base;
+  const uint32_t sK0 = base + kQBytes, sV0 = base + kQBytes + 2 * kKVBytes;  // buffer b is at + b * kKVBytes
+  Barriers *bars = reinterpret_cast<Barriers *>(smem + kQBytes + 4 * kKVBytes);
   volatile int *abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -109,8 +107,9 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
   const int bh = blockIdx.x / n_qtiles;
   const int qi = blockIdx.x % n_qtiles;
   const int qt = causal ? (n_qtiles - 1 - qi) : qi;
-  const int kv_off = Skv - Sq;                                   // causal diagonal offset (multiple of 128)
-  const int nblk = causal ? (qt + kv_off / kBN + 1) : (Skv / kBN);
+  const int kv_off = Skv - Sq;                                    // causal diagonal offset (multiple of 128)
+  const int last_col = qt * kBM + kv_off + kBM - 1;               // last kv column any row of the tile sees
+  const int nblk = causal ? (last_col / kBN + 1) : (Skv / kBN);
   const int q_row0 = bh * Sq + qt * kBM;                          // row in the [B*H*Sq, D] view
   const int kv_row0 = bh * Skv;
 
@@ -118,13 +117,15 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
     bars->abort_flag = 0;
     bars->skip = (status != nullptr && *reinterpret_cast<volatile int *>(status) != 0) ? 1 : 0;
     mbar_init(smem_u32(&bars->q_full), 1);
-    mbar_init(smem_u32(&bars->k_full), 1);
-    mbar_init(smem_u32(&bars->k_empty), 1);
-    mbar_init(smem_u32(&bars->v_full), 1);
-    mbar_init(smem_u32(&bars->v_empty), 1);
-    mbar_init(smem_u32(&bars->s_full), 1);
-    mbar_init(smem_u32(&bars->p_full), kSoftmaxThreads);
-    for (int q4 = 0; q4 < 4; ++q4) mbar_init(smem_u32(&bars->pair[q4]), 64);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&bars->k_full[b]), 1);
+      mbar_init(smem_u32(&bars->k_empty[b]), 1);
+      mbar_init(smem_u32(&bars->v_full[b]), 1);
+      mbar_init(smem_u32(&bars->v_empty[b]), 1);
+      mbar_init(smem_u32(&bars->s_full[b]), 1);
+      mbar_init(smem_u32(&bars->p_full[b]), 128);
+    }
+    mbar_init(smem_u32(&bars->pv_done), 1);
     mbar_init(smem_u32(&bars->o_full), 1);
     fence_barrier_init();
     fence_proxy_async_smem();
@@ -132,11 +133,11 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
   __syncthreads();
   if (bars->skip) return;  // an earlier CTA of this launch already reported a failure
 
-  if (warp == kMmaWarp) {
+  if (warp == 5) {
     tmem_alloc(smem_u32(&bars->tmem_base), kTmemCols);
     tmem_relinquish();
   }
-  if (warp == kProducerWarp && lane == 0) {
+  if (warp == 4 && lane == 0) {
     tma_prefetch_desc(&tm_q);
     tma_prefetch_desc(&tm_k);
     tma_prefetch_desc(&tm_v);
@@ -145,116 +146,150 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = bars->tmem_base;
-  const uint32_t tS = tmem, tO = tmem + kBN;
+  const uint32_t tS0 = tmem, tO = tmem + 2 * kBN;  // S buffer b is at + b * kBN columns
 
-  const uint32_t b_q_full = smem_u32(&bars->q_full), b_k_full = smem_u32(&bars->k_full),
-                 b_k_empty = smem_u32(&bars->k_empty), b_v_full = smem_u32(&bars->v_full),
-                 b_v_empty = smem_u32(&bars->v_empty), b_s_full = smem_u32(&bars->s_full),
-                 b_p_full = smem_u32(&bars->p_full), b_o_full = smem_u32(&bars->o_full);
+  const uint32_t b_q_full = smem_u32(&bars->q_full), b_k_full = smem_u32(&bars->k_full[0]),
+                 b_k_empty = smem_u32(&bars->k_empty[0]), b_v_full = smem_u32(&bars->v_full[0]),
+                 b_v_empty = smem_u32(&bars->v_empty[0]), b_s_full = smem_u32(&bars->s_full[0]),
+                 b_p_full = smem_u32(&bars->p_full[0]), b_pv_done = smem_u32(&bars->pv_done),
+                 b_o_full = smem_u32(&bars->o_full);  // buffer b of a pair is at +8*b
 
-  if (warp == kProducerWarp) {
+  if (warp == 4) {
     // ================================ TMA producer ================================
     if (lane == 0) {
-      mbar_arrive_expect_tx(b_q_full, kTileBytes);
+      mbar_arrive_expect_tx(b_q_full, kQBytes);
       tma_load_2d(sQ, &tm_q, 0, q_row0, b_q_full);
-      tma_load_2d(sQ + kBoxBytes, &tm_q, 64, q_row0, b_q_full);
+      tma_load_2d(sQ + kQBox, &tm_q, 64, q_row0, b_q_full);
       int issued_k = 0, issued_v = 0;
       bool ok = true;
       for (int j = 0; j < nblk && ok; ++j) {
-        const uint32_t ph = j & 1;
-        ok = mbar_wait(b_k_empty, ph ^ 1, abort_flag);
+        const int b = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        ok = mbar_wait(b_k_empty + 8 * b, ph ^ 1, abort_flag);
         if (!ok) { report(status, kErrProducer, 2 * j); break; }
-        mbar_arrive_expect_tx(b_k_full, kTileBytes);
-        tma_load_2d(sK, &tm_k, 0, kv_row0 + j * kBN, b_k_full);
-        tma_load_2d(sK + kBoxBytes, &tm_k, 64, kv_row0 + j * kBN, b_k_full);
+        mbar_arrive_expect_tx(b_k_full + 8 * b, kKVBytes);
+        tma_load_2d(sK0 + b * kKVBytes, &tm_k, 0, kv_row0 + j * kBN, b_k_full + 8 * b);
+        tma_load_2d(sK0 + b * kKVBytes + kKVBox, &tm_k, 64, kv_row0 + j * kBN, b_k_full + 8 * b);
         ++issued_k;
-        ok = mbar_wait(b_v_empty, ph ^ 1, abort_flag);
+        ok = mbar_wait(b_v_empty + 8 * b, ph ^ 1, abort_flag);
         if (!ok) { report(status, kErrProducer, 2 * j + 1); break; }
-        mbar_arrive_expect_tx(b_v_full, kTileBytes);
-        tma_load_2d(sV, &tm_v, 0, kv_row0 + j * kBN, b_v_full);
-        tma_load_2d(sV + kBoxBytes, &tm_v, 64, kv_row0 + j * kBN, b_v_full);
+        mbar_arrive_expect_tx(b_v_full + 8 * b, kKVBytes);
+        tma_load_2d(sV0 + b * kKVBytes, &tm_v, 0, kv_row0 + j * kBN, b_v_full + 8 * b);
+        tma_load_2d(sV0 + b * kKVBytes + kKVBox, &tm_v, 64, kv_row0 + j * kBN, b_v_full + 8 * b);
         ++issued_v;
       }
       if (!ok) {
         // Unwinding: let the copies already in flight land before the CTA's shared memory goes away.
         mbar_wait(b_q_full, 0, abort_flag);
         for (int spin = 0; spin < 100000; ++spin) {
-          const bool kd = issued_k == 0 || mbar_try_wait(b_k_full, (issued_k - 1) & 1);
-          const bool vd = issued_v == 0 || mbar_try_wait(b_v_full, (issued_v - 1) & 1);
-          if (kd && vd) break;
+          bool done = true;
+          for (int n = 0; n < 2; ++n) {  // the last two loads of each kind
+            const int jk = issued_k - 1 - n, jv = issued_v - 1 - n;
+            if (jk >= 0) done = done && mbar_try_wait(b_k_full + 8 * (jk & 1), (jk >> 1) & 1);
+            if (jv >= 0) done = done && mbar_try_wait(b_v_full + 8 * (jv & 1), (jv >> 1) & 1);
+          }
+          if (done) break;
           __nanosleep(100);
         }
       }
     }
     __syncwarp();
-  } else if (warp == kMmaWarp) {
+  } else if (warp == 5) {
     // ================================ MMA issuer ==================================
     if (lane == 0) {
       constexpr int fmt = (DT == NB200_BF16) ? 1 : 0;
       constexpr uint32_t idesc_qk = umma_idesc_f16(fmt, 0, kBM, kBN);
       constexpr uint32_t idesc_pv = umma_idesc_f16(fmt, 1, kBM, kD);
+      // Operand descriptors never change: build them once, so that issuing an MMA is a couple of
+      // instructions (building one per MMA costs ~90 cycles of scalar work and starves the pipe).
+      uint64_t dq[kD / 16], dk[2][kD / 16], dv[2][kBN / 16];
+#pragma unroll
+      for (int kk = 0; kk < kD / 16; ++kk) {
+        // 16 elements of the reduction per MMA = 32 bytes inside the 128-byte swizzled row
+        dq[kk] = umma_desc_sw128(sQ + (kk >> 2) * kQBox + (kk & 3) * 32, 16, 1024);
+#pragma unroll
+        for (int b = 0; b < 2; ++b) dk[b][kk] = umma_desc_sw128(sK0 + b * kKVBytes + (kk >> 2) * kKVBox + (kk & 3) * 32, 16, 1024);
+      }
+#pragma unroll
+      for (int b = 0; b < 2; ++b)
+#pragma unroll
+        for (int kk = 0; kk < kBN / 16; ++kk)  // V: 16 kv rows = 2 KB; the two 64-column blocks are 8 KB apart
+          dv[b][kk] = umma_desc_sw128(sV0 + b * kKVBytes + kk * 2048, kKVBox, 1024);
+
       bool ok = mbar_wait(b_q_full, 0, abort_flag);
       if (!ok) report(status, kErrMma, -1);
-      for (int j = 0; j < nblk && ok; ++j) {
-        const uint32_t ph = j & 1;
-        ok = mbar_wait(b_k_full, ph, abort_flag);
-        if (!ok) { report(status, kErrMma, 3 * j); break; }
-        tc_fence_after();
-#pragma unroll
-        for (int kk = 0; kk < kD / 16; ++kk) {
-          // 16 elements of K per MMA = 32 bytes inside the 128-byte swizzled row
-          const uint32_t off = (kk >> 2) * kBoxBytes + (kk & 3) * 32;
-          umma_ss(tS, umma_desc_sw128(sQ + off, 16, 1024), umma_desc_sw128(sK + off, 16, 1024), idesc_qk,
-                  kk > 0);
-        }
-        umma_commit(b_k_empty);
-        umma_commit(b_s_full);
 
-        // V(j) normally landed long ago; take that wait off the path that follows the softmax
-        ok = mbar_wait(b_v_full, ph, abort_flag);
+      // S_b = Q K(jj)^T for block jj into buffer b = jj & 1
+      auto issue_qk = [&](int jj) -> bool {
+        const int b = jj & 1;
+        if (!mbar_wait(b_k_full + 8 * b, (jj >> 1) & 1, abort_flag)) { report(status, kErrMma, 3 * jj); return false; }
+        tc_fence_after();
+        if (b == 0) {
+#pragma unroll
+          for (int kk = 0; kk < kD / 16; ++kk) umma_ss(tS0, dq[kk], dk[0][kk], idesc_qk, kk > 0);
+        } else {
+#pragma unroll
+          for (int kk = 0; kk < kD / 16; ++kk) umma_ss(tS0 + kBN, dq[kk], dk[1][kk], idesc_qk, kk > 0);
+        }
+        umma_commit(b_k_empty + 8 * b);
+        umma_commit(b_s_full + 8 * b);
+        return true;
+      };
+
+      if (ok) ok = issue_qk(0);
+      if (ok && nblk > 1) ok = issue_qk(1);
+      for (int j = 0; j < nblk && ok; ++j) {
+        const int b = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        ok = mbar_wait(b_v_full + 8 * b, ph, abort_flag);
         if (!ok) { report(status, kErrMma, 3 * j + 2); break; }
-        ok = mbar_wait(b_p_full, ph, abort_flag);
+        ok = mbar_wait(b_p_full + 8 * b, ph, abort_flag);
         if (!ok) { report(status, kErrMma, 3 * j + 1); break; }
         tc_fence_after();
+        // P: 16 packed 16-bit values = 8 TMEM columns per MMA
+        const uint32_t acc0 = j > 0 ? 1u : 0u;
+        if (b == 0) {
 #pragma unroll
-        for (int kk = 0; kk < kBN / 16; ++kk) {
-          // P: 16 packed 16-bit values = 8 TMEM columns; V: 16 kv rows = 2 KB, column blocks 16 KB apart
-          umma_ts(tO, tS + kk * 8, umma_desc_sw128(sV + kk * 2048, kBoxBytes, 1024), idesc_pv,
-                  (j > 0 || kk > 0) ? 1u : 0u);
+          for (int kk = 0; kk < kBN / 16; ++kk) umma_ts(tO, tS0 + kk * 8, dv[0][kk], idesc_pv, kk > 0 ? 1u : acc0);
+        } else {
+#pragma unroll
+          for (int kk = 0; kk < kBN / 16; ++kk) umma_ts(tO, tS0 + kBN + kk * 8, dv[1][kk], idesc_pv, kk > 0 ? 1u : acc0);
         }
-        umma_commit(b_v_empty);
+        umma_commit(b_v_empty + 8 * b);
+        umma_commit(b_pv_done);
+        // S_b is free again (MMAs execute in issue order): start block j+2 into it
+        if (j + 2 < nblk) ok = issue_qk(j + 2);
       }
       if (ok) umma_commit(b_o_full);
     }
     __syncwarp();
   } else {
     // ================================ softmax + epilogue ==========================
-    const int q4 = warp & 3, half = warp >> 2;              // lane quarter, column half
-    const int r = q4 * 32 + lane;                           // row in the tile == TMEM lane
-    const uint32_t lane_addr = static_cast<uint32_t>(q4 * 32) << 16;
-    const int col0 = half * (kBN / 2);                      // this thread's 64 columns of S and of O
-    const uint32_t b_pair = smem_u32(&bars->pair[q4]);
-    const int jdiag = causal ? (nblk - 1) : -1;
+    const int r = warp * 32 + lane;                         // row in the tile == TMEM lane
+    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
     float m_used = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < nblk; ++j) {
+      const int b = j & 1;
       // warp-uniform outcome: the TMEM accesses below are warp-collective
-      ok = __all_sync(0xffffffffu, mbar_wait(b_s_full, j & 1, abort_flag));
+      ok = __all_sync(0xffffffffu, mbar_wait(b_s_full + 8 * b, (j >> 1) & 1, abort_flag));
       if (!ok) { report(status, kErrSoftmax, j); break; }
       tc_fence_after();
-      const bool diag = (j == jdiag);
+      const uint32_t tSb = tS0 + b * kBN + lane_addr;
 
-      // ---- this thread's half row of S into registers (one TMEM read), masked on the diagonal block ----
-      uint32_t v[kBN / 2];
-      tmem_ld32p(tS + lane_addr + col0, v);
-      tmem_ld32p(tS + lane_addr + col0 + 32, v + 32);
+      // ---- the 64 scores of this row into registers (one TMEM read) ----
+      uint32_t v[kBN];
+      tmem_ld32p(tSb, v);
+      tmem_ld32p(tSb + 32, v + 32);
       tmem_wait_ld();
-      if (diag) {
+      // causal: column c of block j is visible to row r iff j*64 + c <= qt*128 + kv_off + r
+      const int vis = causal ? (qt * kBM + kv_off + r - j * kBN) : kBN;  // columns 0..vis are visible
+      if (vis < kBN - 1) {
 #pragma unroll
-        for (int i = 0; i < kBN / 2; ++i) v[i] = (col0 + i > r) ? 0xff800000u : v[i];  // -inf: 2^(-inf) = 0
+        for (int i = 0; i < kBN; ++i) v[i] = (i > vis) ? 0xff800000u : v[i];  // -inf: 2^(-inf) = 0
       }
 
-      // ---- half-row maximum (four chains of three-input maxima), then the partner's half ----
+      // ---- row maximum (four chains of three-input maxima) ----
       float mc[4];
 #pragma unroll
       for (int c = 0; c < 4; ++c)
@@ -267,32 +302,29 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
       }
 #pragma unroll
       for (int c = 0; c < 4; ++c) mc[c] = fmaxf(mc[c], __uint_as_float(v[c * 16 + 15]));
-      float mx = fmaxf(max3(mc[0], mc[1], mc[2]), mc[3]);
-      bars->xmax[j & 1][half][r] = mx;
-      mbar_arrive(b_pair);
-      // Passing this barrier also means the partner has finished reading its columns of S, some of
-      // which this thread's P will overwrite.
-      ok = __all_sync(0xffffffffu, mbar_wait(b_pair, j & 1, abort_flag));
-      if (!ok) { report(status, kErrSoftmax, 1000 + j); break; }
-      mx = fmaxf(mx, bars->xmax[j & 1][half ^ 1][r]);
-      const float m_blk = mx * scale_log2;                   // scale_log2 > 0
+      const float mx = fmaxf(max3(mc[0], mc[1], mc[2]), mc[3]);
+      const float m_blk = mx * scale_log2;                   // scale_log2 > 0; -inf if the whole row is masked
       if (j == 0) {
-        m_used = m_blk;
+        m_used = m_blk;                                      // block 0 always has a visible column
       } else {
         const bool need = m_blk > m_used + kRescaleThreshold;
-        if (__any_sync(0xffffffffu, need)) {                 // same rows, same values: both warps of a pair agree
+        if (__any_sync(0xffffffffu, need)) {
+          // O must hold every product up to block j-1 and none may be in flight.  S(j) was issued
+          // after PV(j-2), so only PV(j-1) can be outstanding: its completion is phase j-1 of pv_done.
+          ok = __all_sync(0xffffffffu, mbar_wait(b_pv_done, (j - 1) & 1, abort_flag));
+          if (!ok) { report(status, kErrSoftmax, 1000 + j); break; }
+          tc_fence_after();
           const float f = need ? ex2(m_used - m_blk) : 1.f;
           if (need) m_used = m_blk;
           l *= f;
-          // PV(j-1) has retired: the commit that signalled s_full(j) was issued after it.
 #pragma unroll 1
-          for (int c = 0; c < 4; ++c) {  // 16 columns at a time: the half row of S stays live in registers
+          for (int c = 0; c < kD / 16; ++c) {  // 16 columns at a time: the scores stay live in registers
             uint32_t o[16];
-            tmem_ld16(tO + lane_addr + col0 + c * 16, o);
+            tmem_ld16(tO + lane_addr + c * 16, o);
             tmem_wait_ld();
 #pragma unroll
             for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
-            tmem_st16(tO + lane_addr + col0 + c * 16, o);
+            tmem_st16(tO + lane_addr + c * 16, o);
           }
           tmem_wait_st();
         }
@@ -302,7 +334,7 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
       const uint64_t c2 = f2_pack(scale_log2, scale_log2), nm2 = f2_pack(-m_used, -m_used);
       uint64_t lsum2 = f2_pack(0.f, 0.f);
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      for (int c = 0; c < kBN / 32; ++c) {
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
@@ -321,7 +353,7 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
           lsum2 = f2_add(lsum2, f2_pack(p0, p1));
           pk[i] = pack2<DT>(p0, p1);
         }
-        tmem_st16(tS + lane_addr + col0 / 2 + c * 16, pk);   // 64 columns of S -> 32 packed columns of P
+        tmem_st16(tSb + c * 16, pk);
       }
       {
         const float2 ls = f2_unpack(lsum2);
@@ -329,29 +361,22 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
       }
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(b_p_full);
+      mbar_arrive(b_p_full + 8 * b);
     }
 
-    // ---- epilogue: O / l -> storage dtype -> global; each thread writes its 64 columns ----
+    // ---- epilogue: O / l -> storage dtype -> global ----
     if (ok) {
-      bars->xsum[half][r] = l;
-      mbar_arrive(b_pair);
-      ok = __all_sync(0xffffffffu, mbar_wait(b_pair, nblk & 1, abort_flag));
-      if (!ok) report(status, kErrEpilogue, 1);
-    }
-    if (ok) {
-      l += bars->xsum[half ^ 1][r];
       ok = __all_sync(0xffffffffu, mbar_wait(b_o_full, 0, abort_flag));
       if (!ok) report(status, kErrEpilogue, 0);
     }
     if (ok) {
       tc_fence_after();
       const float inv = 1.f / l;
-      uint16_t *dst = out + (static_cast<size_t>(q_row0) + r) * kD + col0;
+      uint16_t *dst = out + (static_cast<size_t>(q_row0) + r) * kD;
 #pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
+      for (int c = 0; c < kD / 32; ++c) {
         uint32_t o[32];
-        tmem_ld32(tO + lane_addr + col0 + c * 32, o);
+        tmem_ld32(tO + lane_addr + c * 32, o);
         tmem_wait_ld();
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -369,7 +394,7 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
   // ================================ tear-down =====================================
   tc_fence_before();
   __syncthreads();
-  if (warp == kMmaWarp) {
+  if (warp == 5) {
     tc_fence_after();
     tmem_dealloc(tmem, kTmemCols);
   }
@@ -393,13 +418,13 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
-// [rows, 128] 16-bit row-major tensor, boxes of 128 rows x 64 columns, 128-byte swizzle.
-int make_tile_map(CUtensorMap *tm, const void *ptr, long long rows, int dtype) {
+// [rows, 128] 16-bit row-major tensor, boxes of box_rows rows x 64 columns, 128-byte swizzle.
+int make_tile_map(CUtensorMap *tm, const void *ptr, long long rows, int dtype, int box_rows) {
   EncodeTiledFn enc = encode_tiled_fn();
   NB200_REQUIRE(enc, NB200_ERR_LAUNCH, "attn_fwd: cuTensorMapEncodeTiled is not available from the driver");
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(kD), static_cast<cuuint64_t>(rows)};
   const cuuint64_t strides[1] = {static_cast<cuuint64_t>(kD) * 2};
-  const cuuint32_t box[2] = {64, static_cast<cuuint32_t>(kBM)};
+  const cuuint32_t box[2] = {64, static_cast<cuuint32_t>(box_rows)};
   const cuuint32_t estr[2] = {1, 1};
   const CUresult r = enc(tm, dtype == NB200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
                          2, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -415,7 +440,7 @@ int launch_tc(const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &t
   // per-device attribute: set on every call so that any current device is covered
   NB200_CHECK_CUDA(cudaFuncSetAttribute(attn_fwd_tcgen05_kernel<DT, POLY>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         kSmemBytes));
-  // two CTAs of ~98 KB must fit: ask for the largest shared-memory carve-out
+  // two CTAs of ~97 KB must fit: ask for the largest shared-memory carve-out
   NB200_CHECK_CUDA(cudaFuncSetAttribute(attn_fwd_tcgen05_kernel<DT, POLY>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                         cudaSharedmemCarveoutMaxShared));
   const int n_qtiles = Sq / kBM;
@@ -445,7 +470,7 @@ extern "C" int nb200_attn_fwd(const void *q, const void *k, const void *v, void 
                 "attn_fwd: dtype %d", dtype);
   auto st = static_cast<cudaStream_t>(stream);
   const bool tensor_path = (dtype == NB200_F16 || dtype == NB200_BF16) && D == kD && Sq % kBM == 0 &&
-                           Skv % kBN == 0 && (long long)B * H * (Sq / kBM) < (1ll << 31) &&
+                           Skv % kBM == 0 && (long long)B * H * (Sq / kBM) < (1ll << 31) &&
                            (long long)B * H * (long long)(Sq > Skv ? Sq : Skv) < (1ll << 31);
   if (!tensor_path) return attn_simt_launch(q, k, v, out, B, H, Sq, Skv, D, dtype, scale_log2, causal, st);
 
@@ -453,9 +478,9 @@ extern "C" int nb200_attn_fwd(const void *q, const void *k, const void *v, void 
                 "attn_fwd: tensors must be 16-byte aligned");
   CUtensorMap tq, tk, tv;
   int rc;
-  if ((rc = make_tile_map(&tq, q, (long long)B * H * Sq, dtype)) != NB200_OK) return rc;
-  if ((rc = make_tile_map(&tk, k, (long long)B * H * Skv, dtype)) != NB200_OK) return rc;
-  if ((rc = make_tile_map(&tv, v, (long long)B * H * Skv, dtype)) != NB200_OK) return rc;
+  if ((rc = make_tile_map(&tq, q, (long long)B * H * Sq, dtype, kBM)) != NB200_OK) return rc;
+  if ((rc = make_tile_map(&tk, k, (long long)B * H * Skv, dtype, kBN)) != NB200_OK) return rc;
+  if ((rc = make_tile_map(&tv, v, (long long)B * H * Skv, dtype, kBN)) != NB200_OK) return rc;
   static const int poly = [] {
     const char *e = getenv("NB200_ATTN_POLY");
     return e ? atoi(e) : 0;
