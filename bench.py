@@ -309,6 +309,7 @@ def bench_extra(args, d: Dist, dev, flush, pk, pk_kind) -> dict:
 
     steps, warm = max(3, min(args.steps, 10)), 3
     hbm = pk["hbm_gbs"]
+    want = set(args.extra.split(","))
     out: dict = {}
     gen = torch.Generator(device=dev).manual_seed(3000 + d.rank)
     bf = torch.bfloat16
@@ -323,97 +324,106 @@ def bench_extra(args, d: Dist, dev, flush, pk, pk_kind) -> dict:
                                   "frac": gbs / d.world / hbm, "peak_source": f"of {pk_kind} (copy)"}} | (extra or {})
 
     # -- split-K decode, batch sharded over ranks
-    c = DECODE
-    lo, hi = shard_range(c["B"], d.rank, d.world)
-    Bl = hi - lo
-    fn = load_callable(programs.decode_splitk_decl("decode", Bl, c["Hq"], c["Hkv"], c["L"], c["D"], c["S"]), "decode")
-    q, k, v = rnd((Bl, c["Hq"], c["D"])), rnd((Bl, c["Hkv"], c["L"], c["D"])), rnd((Bl, c["Hkv"], c["L"], c["D"]))
-    part = torch.empty((Bl, c["Hq"], c["S"], c["D"] + 2), device=dev)
-    o = torch.empty_like(q)
-    ms = timed_steps(lambda: fn(q, k, v, part, o), steps, warm, flush, d)
-    total = 2 * c["B"] * c["Hkv"] * c["L"] * c["D"] * 2 + 2 * c["B"] * c["Hq"] * c["D"] * 2
-    record("decode_splitk", ms, total, {"config": "B=64 Hq=32 Hkv=8 L=32768 D=128, 16 splits (configs[2])", "launches_per_step": 2})
-    del q, k, v, part, o
-    torch.cuda.empty_cache()
+    def run_decode():
+        c = DECODE
+        lo, hi = shard_range(c["B"], d.rank, d.world)
+        Bl = hi - lo
+        fn = load_callable(programs.decode_splitk_decl("decode", Bl, c["Hq"], c["Hkv"], c["L"], c["D"], c["S"]), "decode")
+        q, k, v = rnd((Bl, c["Hq"], c["D"])), rnd((Bl, c["Hkv"], c["L"], c["D"])), rnd((Bl, c["Hkv"], c["L"], c["D"]))
+        part = torch.empty((Bl, c["Hq"], c["S"], c["D"] + 2), device=dev)
+        o = torch.empty_like(q)
+        ms = timed_steps(lambda: fn(q, k, v, part, o), steps, warm, flush, d)
+        total = 2 * c["B"] * c["Hkv"] * c["L"] * c["D"] * 2 + 2 * c["B"] * c["Hq"] * c["D"] * 2
+        record("decode_splitk", ms, total, {"config": "B=64 Hq=32 Hkv=8 L=32768 D=128, 16 splits (configs[2])", "launches_per_step": 2})
+        del q, k, v, part, o
+        torch.cuda.empty_cache()
 
     # -- single sequence, KV sharded along L over ranks, partials merged over NCCL
-    c = DECODE1
-    lo, hi = shard_range(c["L"], d.rank, d.world)
-    Ll = hi - lo
-    rows = c["Hq"]
-    q = rnd((1, c["Hq"], c["D"]))
-    if d.world > 1:
-        dist.broadcast(q, src=0)
-    k, v = rnd((1, c["Hkv"], Ll, c["D"])), rnd((1, c["Hkv"], Ll, c["D"]))
-    part = torch.empty((1, c["Hq"], c["S"], c["D"] + 2), device=dev)
-    local = torch.empty((rows, c["D"] + 2), device=dev)
-    o = torch.empty((rows, c["D"]), device=dev, dtype=bf)
-    scale_log2 = math.log2(math.e) / math.sqrt(c["D"])
-    from neptune_mlir import native
-    lib = native.lib()
-
-    def stream_part():
-        st = torch.cuda.current_stream(dev).cuda_stream
-        native.check(lib.nb200_decode_splitk(q.data_ptr(), k.data_ptr(), v.data_ptr(), part.data_ptr(), 1, c["Hq"], c["Hkv"],
-                                             Ll, c["D"], c["S"], 1, scale_log2, st), "decode_splitk")
-        runtime.decode_combine(part, local, rows=rows, D=c["D"], n_splits=c["S"], row_stride=c["S"] * (c["D"] + 2),
-                               split_stride=c["D"] + 2, out_dtype="f32")
-
-    def merge_part():
+    def run_decode1():
+        c = DECODE1
+        lo, hi = shard_range(c["L"], d.rank, d.world)
+        Ll = hi - lo
+        rows = c["Hq"]
+        q = rnd((1, c["Hq"], c["D"]))
         if d.world > 1:
-            g = gather_partials(local)
-            rs, ss = gathered_strides(rows, c["D"] + 2)
-            runtime.decode_combine(g, o, rows=rows, D=c["D"], n_splits=d.world, row_stride=rs, split_stride=ss, out_dtype="bf16")
-        else:
-            runtime.decode_combine(local, o, rows=rows, D=c["D"], n_splits=1, row_stride=c["D"] + 2,
-                                   split_stride=c["D"] + 2, out_dtype="bf16")
+            dist.broadcast(q, src=0)
+        k, v = rnd((1, c["Hkv"], Ll, c["D"])), rnd((1, c["Hkv"], Ll, c["D"]))
+        part = torch.empty((1, c["Hq"], c["S"], c["D"] + 2), device=dev)
+        local = torch.empty((rows, c["D"] + 2), device=dev)
+        o = torch.empty((rows, c["D"]), device=dev, dtype=bf)
+        scale_log2 = math.log2(math.e) / math.sqrt(c["D"])
+        from neptune_mlir import native
+        lib = native.lib()
 
-    ms_stream = timed_steps(stream_part, steps, warm, flush, d)
-    ms_merge = timed_steps(merge_part, steps, warm, flush, d)
-    ms_both = timed_steps(lambda: (stream_part(), merge_part()), steps, warm, flush, d)
-    total = 2 * c["Hkv"] * c["L"] * c["D"] * 2 + 2 * c["Hq"] * c["D"] * 2
-    record("decode_single_sequence", ms_both, total,
-           {"config": "B=1 L=262144 KV sharded along L over ranks (configs[2] variant)", "stream_ms": ms_stream,
-            "merge_ms": ms_merge, "merge_bytes_per_rank": rows * (c["D"] + 2) * 4,
-            "collective": "all_gather (NCCL)" if d.world > 1 else "none"})
-    del q, k, v, part, local, o
-    torch.cuda.empty_cache()
+        def stream_part():
+            st = torch.cuda.current_stream(dev).cuda_stream
+            native.check(lib.nb200_decode_splitk(q.data_ptr(), k.data_ptr(), v.data_ptr(), part.data_ptr(), 1, c["Hq"], c["Hkv"],
+                                                 Ll, c["D"], c["S"], 1, scale_log2, st), "decode_splitk")
+            runtime.decode_combine(part, local, rows=rows, D=c["D"], n_splits=c["S"], row_stride=c["S"] * (c["D"] + 2),
+                                   split_stride=c["D"] + 2, out_dtype="f32")
+
+        def merge_part():
+            if d.world > 1:
+                g = gather_partials(local)
+                rs, ss = gathered_strides(rows, c["D"] + 2)
+                runtime.decode_combine(g, o, rows=rows, D=c["D"], n_splits=d.world, row_stride=rs, split_stride=ss, out_dtype="bf16")
+            else:
+                runtime.decode_combine(local, o, rows=rows, D=c["D"], n_splits=1, row_stride=c["D"] + 2,
+                                       split_stride=c["D"] + 2, out_dtype="bf16")
+
+        ms_stream = timed_steps(stream_part, steps, warm, flush, d)
+        ms_merge = timed_steps(merge_part, steps, warm, flush, d)
+        ms_both = timed_steps(lambda: (stream_part(), merge_part()), steps, warm, flush, d)
+        total = 2 * c["Hkv"] * c["L"] * c["D"] * 2 + 2 * c["Hq"] * c["D"] * 2
+        record("decode_single_sequence", ms_both, total,
+               {"config": "B=1 L=262144 KV sharded along L over ranks (configs[2] variant)", "stream_ms": ms_stream,
+                "merge_ms": ms_merge, "merge_bytes_per_rank": rows * (c["D"] + 2) * 4,
+                "collective": "all_gather (NCCL)" if d.world > 1 else "none"})
+        del q, k, v, part, local, o
+        torch.cuda.empty_cache()
 
     # -- Mamba-1 selective scan, (batch x channel) rows sharded as whole sequences when possible, else channels
-    c = SCAN
-    if c["B"] % d.world == 0:
-        Bl, Dl = c["B"] // d.world, c["Dm"]
-    else:
-        Bl, Dl = c["B"], c["Dm"] // d.world
-    fn = load_callable(programs.selective_scan_decl("scan", Bl, Dl, c["L"], c["N"]), "scan")
-    u, z = rnd((Bl, Dl, c["L"])), rnd((Bl, Dl, c["L"]))
-    delta = torch.nn.functional.softplus(rnd((Bl, Dl, c["L"]), torch.float32) - 4.0).to(bf)
-    A = -torch.exp(torch.rand((Dl, c["N"]), device=dev, generator=gen) * math.log(16.0))
-    Bm, Cm = rnd((Bl, c["N"], c["L"])), rnd((Bl, c["N"], c["L"]))
-    Dk = rnd((Dl,), torch.float32)
-    o = torch.empty_like(u)
-    ms = timed_steps(lambda: fn(u, delta, A, Bm, Cm, Dk, z, o), steps, warm, flush, d)
-    total = 4 * c["B"] * c["Dm"] * c["L"] * 2 + 2 * c["B"] * c["N"] * c["L"] * 2 + c["Dm"] * c["N"] * 4 + c["Dm"] * 4
-    record("selective_scan", ms, total, {"config": "B=8 D=4096 L=4096 N=16 (configs[3])", "launches_per_step": 1,
-                                         "state_updates_per_s": c["B"] * c["Dm"] * c["L"] * c["N"] / (ms * 1e-3)})
-    del u, z, delta, A, Bm, Cm, Dk, o
-    torch.cuda.empty_cache()
+    def run_scan():
+        c = SCAN
+        if c["B"] % d.world == 0:
+            Bl, Dl = c["B"] // d.world, c["Dm"]
+        else:
+            Bl, Dl = c["B"], c["Dm"] // d.world
+        fn = load_callable(programs.selective_scan_decl("scan", Bl, Dl, c["L"], c["N"]), "scan")
+        u, z = rnd((Bl, Dl, c["L"])), rnd((Bl, Dl, c["L"]))
+        delta = torch.nn.functional.softplus(rnd((Bl, Dl, c["L"]), torch.float32) - 4.0).to(bf)
+        A = -torch.exp(torch.rand((Dl, c["N"]), device=dev, generator=gen) * math.log(16.0))
+        Bm, Cm = rnd((Bl, c["N"], c["L"])), rnd((Bl, c["N"], c["L"]))
+        Dk = rnd((Dl,), torch.float32)
+        o = torch.empty_like(u)
+        ms = timed_steps(lambda: fn(u, delta, A, Bm, Cm, Dk, z, o), steps, warm, flush, d)
+        total = 4 * c["B"] * c["Dm"] * c["L"] * 2 + 2 * c["B"] * c["N"] * c["L"] * 2 + c["Dm"] * c["N"] * 4 + c["Dm"] * 4
+        record("selective_scan", ms, total, {"config": "B=8 D=4096 L=4096 N=16 (configs[3])", "launches_per_step": 1,
+                                             "state_updates_per_s": c["B"] * c["Dm"] * c["L"] * c["N"] / (ms * 1e-3)})
+        del u, z, delta, A, Bm, Cm, Dk, o
+        torch.cuda.empty_cache()
 
     # -- Mamba-2 SSD, heads sharded over ranks
-    c = SSD
-    lo, hi = shard_range(c["H"], d.rank, d.world)
-    Hl = hi - lo
-    ws_bytes = runtime.ssd_workspace_bytes(c["B"], c["L"], Hl, c["P"], c["N"], c["G"], c["chunk"])
-    fn = load_callable(programs.ssd_chunk_scan_decl("ssd", c["B"], c["L"], Hl, c["P"], c["N"], c["G"], c["chunk"], ws_bytes), "ssd")
-    x = rnd((c["B"], c["L"], Hl, c["P"]))
-    dt = torch.nn.functional.softplus(rnd((c["B"], c["L"], Hl), torch.float32))
-    A = -torch.exp(torch.rand((Hl,), device=dev, generator=gen) * math.log(16.0))
-    Bm, Cm = rnd((c["B"], c["L"], c["G"], c["N"])), rnd((c["B"], c["L"], c["G"], c["N"]))
-    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
-    y = torch.empty_like(x)
-    ms = timed_steps(lambda: fn(x, dt, A, Bm, Cm, ws, y), steps, warm, flush, d)
-    total = 2 * c["B"] * c["L"] * c["H"] * c["P"] * 2 + c["B"] * c["L"] * c["H"] * 4 + 2 * c["B"] * c["L"] * c["G"] * c["N"] * 2 + c["H"] * 4
-    record("ssd_chunk_scan", ms, total, {"config": "B=4 L=8192 H=64 P=64 N=128 chunk=256 (configs[4])", "launches_per_step": 3})
+    def run_ssd():
+        c = SSD
+        lo, hi = shard_range(c["H"], d.rank, d.world)
+        Hl = hi - lo
+        ws_bytes = runtime.ssd_workspace_bytes(c["B"], c["L"], Hl, c["P"], c["N"], c["G"], c["chunk"])
+        fn = load_callable(programs.ssd_chunk_scan_decl("ssd", c["B"], c["L"], Hl, c["P"], c["N"], c["G"], c["chunk"], ws_bytes), "ssd")
+        x = rnd((c["B"], c["L"], Hl, c["P"]))
+        dt = torch.nn.functional.softplus(rnd((c["B"], c["L"], Hl), torch.float32))
+        A = -torch.exp(torch.rand((Hl,), device=dev, generator=gen) * math.log(16.0))
+        Bm, Cm = rnd((c["B"], c["L"], c["G"], c["N"])), rnd((c["B"], c["L"], c["G"], c["N"]))
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+        y = torch.empty_like(x)
+        ms = timed_steps(lambda: fn(x, dt, A, Bm, Cm, ws, y), steps, warm, flush, d)
+        total = 2 * c["B"] * c["L"] * c["H"] * c["P"] * 2 + c["B"] * c["L"] * c["H"] * 4 + 2 * c["B"] * c["L"] * c["G"] * c["N"] * 2 + c["H"] * 4
+        record("ssd_chunk_scan", ms, total, {"config": "B=4 L=8192 H=64 P=64 N=128 chunk=256 (configs[4])", "launches_per_step": 3})
+
+    for name, fn_ in (("decode", run_decode), ("decode1", run_decode1), ("scan", run_scan), ("ssd", run_ssd)):
+        if name in want:
+            fn_()
+            torch.cuda.empty_cache()
     return out
 
 
@@ -424,7 +434,11 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=("native", "reference"), default="native")
     ap.add_argument("--skip-extra", action="store_true", help="attention only (skip decode and the scans)")
+    ap.add_argument("--extra", default="decode,decode1,scan,ssd",
+                    help="comma list of the secondary workloads to run (decode, decode1, scan, ssd)")
     ap.add_argument("--skip-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--skip-attention", action="store_true",
+                    help="secondary workloads only (profiler captures of decode and the scans)")
     ap.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     ap.add_argument("--attn-units", type=int, default=0,
                     help="number of (batch, head) units of the attention workload (default: the full 256); "
@@ -455,7 +469,10 @@ def main() -> None:
                          "oracle attention_reference (the reference's check math plus the causal mask) on CPU tensors"}
     d.barrier()
 
-    attn = bench_attention(args, d, dev, flush, pk, pk_kind)
+    if args.skip_attention:
+        attn = {"value": None, "ms": None, "roofline": None, "e2e": None, "gpu_launches": 0, "clocks": None}
+    else:
+        attn = bench_attention(args, d, dev, flush, pk, pk_kind)
     extra = {} if args.skip_extra else bench_extra(args, d, dev, flush, pk, pk_kind)
 
     if d.rank == 0:
