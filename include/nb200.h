@@ -140,8 +140,12 @@ int nb200_selective_scan_fwd(const void *u, const void *delta, const float *A, c
  * Mamba-2 SSD chunked scan forward (no counterpart in the reference).
  *   x, y : [B, L, H, P]   dt : fp32 [B, L, H] (already soft-plused)   A : fp32 [H]
  *   Bm, Cm : [B, L, G, N]  (head h reads group h / (H / G))
- *   workspace : nb200_ssd_workspace_bytes(...) bytes of device memory (chunk states and decays)
- * P == 64, N == 128, chunk in {64, 128, 256}, L a multiple of chunk.
+ *   workspace : nb200_ssd_workspace_bytes(...) bytes of device memory.  The recurrent state stays on
+ *               chip, so this is only a status buffer (NB200_STATUS_WORDS int32) that the call clears
+ *               and in which an expired device-side wait is recorded; read it with nb200_status_read.
+ * P == 64, N == 128, chunk in {64, 128, 256}, L a multiple of 128 and of chunk.  The kernel walks the
+ * sequence in steps of 128 rows whatever `chunk` says; the result does not depend on the chunk length
+ * beyond rounding.
  */
 size_t nb200_ssd_workspace_bytes(int B, int L, int H, int P, int N, int G, int chunk);
 

@@ -198,6 +198,11 @@ __host__ __device__ constexpr uint32_t umma_idesc_f16(int ab_format, int b_mn_ma
          (static_cast<uint32_t>(M >> 4) << 24);
 }
 
+// Same, with the A operand's major-ness explicit (a_mn_major only for an A operand in shared memory).
+__host__ __device__ constexpr uint32_t umma_idesc_f16_ab(int ab_format, int a_mn_major, int b_mn_major, int M, int N) {
+  return umma_idesc_f16(ab_format, b_mn_major, M, N) | (static_cast<uint32_t>(a_mn_major) << 15);
+}
+
 // D[tmem] (+)= A[smem] * B[smem]; issued by one thread.
 __device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                         uint32_t accumulate) {

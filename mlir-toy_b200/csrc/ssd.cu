@@ -1,330 +1,421 @@
-// Mamba-2 SSD chunked scan forward.
+// Mamba-2 SSD scan forward, fused into one kernel with the state kept on chip.
 //
 //   S <- exp(dt*A) S + dt * x (outer) B ;   y = S . C        (S is P x N per (batch, head))
 //
-// evaluated chunk by chunk (chunk length Q), with cum_i = sum_{s<=i} dt_s*A inside a chunk:
-//   kernel 1  per (b, chunk, head): cum -> workspace; chunk state
-//             Z = sum_j e^(cum_Q - cum_j) dt_j x_j (outer) B_j            (tensor cores, fp32 accumulate)
-//   kernel 2  per (b, head): the fp32 recurrence S_in(c) = e^(cum_Q(c-1)) S_in(c-1) + Z(c-1), in place
-//   kernel 3  per (b, chunk, head, 64-row block): y = e^(cum_i) C_i . S_in
-//             + sum_{j<=i} (C_i . B_j) e^(cum_i - cum_j) dt_j x_j         (tensor cores, fp32 accumulate)
-// All exponents are <= 0 (A < 0), so nothing overflows.  Matrix products run on warp-level bf16/f16
-// MMA (16x16x16 fragments) with fp32 accumulation; decay factors are applied in fp32 between the
-// two products of kernel 3 and the masked product is rounded to the storage dtype before it
-// multiplies x, exactly as the CPU oracle's chunked form does.
-#include <mma.h>
+// One CTA owns one (batch, head) and walks the sequence in steps of 128 rows; the fp32 state
+// S (N x P = 128 x 64) never leaves tensor memory, x is read once and y written once.  With
+// cum_i = sum_{s<=i} dt_s*A inside a step (kept in the log2 domain) a step is four tensor-core
+// products and three element-wise passes:
+//
+//   Y  = (C_i e^cum_i) . S_in                A: C rows scaled by their decay, 16-bit in TMEM; B: S_in
+//                                            rounded to 16 bit in shared memory            (128x64x128)
+//   G  = C . B^T                             both operands TMA tiles in shared memory      (128x128x128)
+//   S  = e^cum_last S + B^T . (w x)          w_j = e^(cum_last - cum_j) dt_j; both operands MN-major
+//                                            shared-memory tiles, accumulator = the state  (128x64x128)
+//   Y += (G o decay o mask) . x              decay_ij = e^(cum_i - cum_j) dt_j for j <= i; A is G
+//                                            overwritten in place as 16-bit in TMEM        (128x64x128)
+//
+//   warps 0-3   thread i = row i of the step = TMEM lane i: prefix sum of dt*A (each warp scans all
+//               128 values itself, so no cross-warp exchange), the scaled copies of C, x and S, the
+//               decay/mask pass over G, and the epilogue (Y -> 16 bit -> global)
+//   warp 4      TMA producer: B, C (two 64-column boxes each) and x tiles of the next step
+//   warp 5      MMA issuer, operand descriptors built once
+//
+// All exponents are <= 0 (A < 0), so nothing overflows.  TMEM: columns 0-127 hold C e^cum, then G,
+// then the masked product (each overwriting the previous), 128-191 Y, 192-255 the state; two CTAs
+// fit per SM.  Every wait is bounded and reports through the status words.
+#include <cuda.h>
 
 #include "nb200_common.cuh"
+#include "sm100_primitives.cuh"
+#include "tma_host.cuh"
 
 namespace nb200 {
 namespace {
 
-using namespace nvcuda;
+using namespace sm100;
 
-constexpr int kP = 64;     // head dimension
-constexpr int kN = 128;    // state dimension
-constexpr int kJB = 64;    // rows per staged block
-constexpr int kLdN = kN + 8;   // padded leading dimensions (elements)
-constexpr int kLdP = kP + 8;
-constexpr int kLdG = kJB + 4;  // fp32 scratch
+constexpr int kQ = 128;          // rows per step
+constexpr int kP = 64;           // head dimension
+constexpr int kN = 128;          // state dimension
+constexpr int kSsdThreads = 192;
+constexpr int kBCBytes = kQ * kN * 2;      // 32 KB: two 64-column boxes of 16 KB
+constexpr int kBCBox = kBCBytes / 2;
+constexpr int kXBytes = kQ * kP * 2;       // 16 KB: one box
+constexpr int kTileBytes = 2 * kBCBytes + kXBytes;
+constexpr int kSsdSmem = 2 * kBCBytes + 2 * kXBytes + 4 * kQ * 4 /*lb*/ + 256 /*barriers*/;
+constexpr int kSsdTmemCols = 256;
 constexpr float kLog2e = 1.4426950408889634f;
 
-template <int DT> struct WmmaElem;
-template <> struct WmmaElem<NB200_F16> { using type = __half; };
-template <> struct WmmaElem<NB200_BF16> { using type = __nv_bfloat16; };
+enum : int { kErrSsdProducer = 11, kErrSsdMma = 12, kErrSsdCompute = 13, kErrSsdAlign = 15 };
 
-template <int DT> __device__ __forceinline__ typename WmmaElem<DT>::type to_elem(float x);
-template <> __device__ __forceinline__ __half to_elem<NB200_F16>(float x) { return __float2half_rn(x); }
-template <> __device__ __forceinline__ __nv_bfloat16 to_elem<NB200_BF16>(float x) { return __float2bfloat16_rn(x); }
+struct SsdBarriers {
+  uint64_t tile_full, tiles_free, e1a, inter_done, e1b, g_ready, m_ready, y_ready;
+  uint32_t tmem_base;
+  int abort_flag;
+  int skip;
+};
 
-// ---- kernel 1: cumulative decay and chunk state -------------------------------------------------
+__device__ __forceinline__ void ssd_report(int *status, int code, int detail) {
+  if (status && atomicCAS(status, 0, code) == 0) {
+    status[1] = static_cast<int>(blockIdx.x);
+    status[2] = detail;
+    status[3] = static_cast<int>(threadIdx.x);
+  }
+}
+
+__device__ __forceinline__ float lg2(float x) {
+  float y;
+  asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Byte offset of 16-byte chunk `c` of row `r` inside a 128-byte-swizzled box (rows of 128 bytes).
+__device__ __forceinline__ uint32_t sw128(int r, int c) { return r * 128 + ((c ^ (r & 7)) << 4); }
+
 template <int DT>
-__global__ void __launch_bounds__(128)
-ssd_chunk_state_kernel(const uint16_t *__restrict__ x, const float *__restrict__ dt, const float *__restrict__ A,
-                       const uint16_t *__restrict__ Bm, float *__restrict__ cum_ws, float *__restrict__ state_ws,
-                       int L, int H, int G, int Q) {
-  using T = typename WmmaElem<DT>::type;
-  extern __shared__ __align__(128) unsigned char smem_raw[];
-  T *sXs = reinterpret_cast<T *>(smem_raw);                        // [kJB][kLdP]  w_j * x_j
-  T *sB = sXs + kJB * kLdP;                                        // [kJB][kLdN]
-  float *sCum = reinterpret_cast<float *>(sB + kJB * kLdN);        // [Q]
-  float *sW = sCum + Q;                                            // [Q]  e^(cum_Q - cum_j) dt_j
+__global__ void __launch_bounds__(kSsdThreads, 2)
+ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_b,
+                 const __grid_constant__ CUtensorMap tm_c, const float *__restrict__ dt, const float *__restrict__ A,
+                 uint16_t *__restrict__ y, int L, int H, int G, int *status) {
+  extern __shared__ __align__(1024) unsigned char smem[];
+  const uint32_t base = smem_u32(smem);
+  if ((base & 1023u) != 0) {
+    if (threadIdx.x == 0) ssd_report(status, kErrSsdAlign, static_cast<int>(base));
+    return;
+  }
+  const uint32_t sB = base, sC = base + kBCBytes, sX = base + 2 * kBCBytes, sXs = sX + kXBytes;
+  unsigned char *pC = smem + kBCBytes, *pX = smem + 2 * kBCBytes, *pXs = pX + kXBytes;
+  float *lb_all = reinterpret_cast<float *>(smem + 2 * kBCBytes + 2 * kXBytes);  // [4 warps][128]
+  SsdBarriers *bars = reinterpret_cast<SsdBarriers *>(smem + 2 * kBCBytes + 2 * kXBytes + 4 * kQ * 4);
+  volatile int *abort_flag = &bars->abort_flag;
 
-  const int h = blockIdx.x, c = blockIdx.y, b = blockIdx.z;
-  const int nc = L / Q;
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = blockIdx.x % H, b = blockIdx.x / H;
   const int g = h / (H / G);
-  const size_t t0 = (size_t)b * L + (size_t)c * Q;                 // first time step of the chunk (row index)
-  const float a = A[h];
+  const int nsteps = L / kQ;
 
-  // inclusive prefix sum of dt*A over the chunk: warp 0, Q/32 consecutive values per lane
-  if (warp == 0) {
-    const int per = Q / 32;
-    float run = 0.f;
-    for (int i = 0; i < per; ++i) {
-      run += dt[(t0 + lane * per + i) * H + h] * a;
-      sCum[lane * per + i] = run;
-    }
-    float offs = run;
-#pragma unroll
-    for (int d = 1; d < 32; d <<= 1) {
-      const float o = __shfl_up_sync(0xffffffffu, offs, d);
-      if (lane >= d) offs += o;
-    }
-    offs -= run;  // exclusive prefix of the lane totals
-    for (int i = 0; i < per; ++i) sCum[lane * per + i] += offs;
+  if (threadIdx.x == 0) {
+    bars->abort_flag = 0;
+    bars->skip = (status != nullptr && *reinterpret_cast<volatile int *>(status) != 0) ? 1 : 0;
+    mbar_init(smem_u32(&bars->tile_full), 1);
+    mbar_init(smem_u32(&bars->tiles_free), 1);
+    mbar_init(smem_u32(&bars->e1a), 128);
+    mbar_init(smem_u32(&bars->inter_done), 1);
+    mbar_init(smem_u32(&bars->e1b), 128);
+    mbar_init(smem_u32(&bars->g_ready), 1);
+    mbar_init(smem_u32(&bars->m_ready), 128);
+    mbar_init(smem_u32(&bars->y_ready), 1);
+    fence_barrier_init();
+    fence_proxy_async_smem();
   }
   __syncthreads();
-  const float cum_last = sCum[Q - 1];
-  float *cum_out = cum_ws + (((size_t)b * H + h) * nc + c) * Q;
-  for (int i = tid; i < Q; i += 128) {
-    const float ci = sCum[i];
-    cum_out[i] = ci;
-    sW[i] = ex2((cum_last - ci) * kLog2e) * dt[(t0 + i) * H + h];
+  if (bars->skip) return;
+
+  if (warp == 5) {
+    tmem_alloc(smem_u32(&bars->tmem_base), kSsdTmemCols);
+    tmem_relinquish();
   }
+  if (warp == 4 && lane == 0) {
+    tma_prefetch_desc(&tm_x);
+    tma_prefetch_desc(&tm_b);
+    tma_prefetch_desc(&tm_c);
+  }
+  tc_fence_before();
   __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars->tmem_base;
+  const uint32_t tR = tmem, tY = tmem + 128, tS = tmem + 192;
 
-  // Z[p][n] = sum_j Xs[j][p] * B[j][n]; warp w owns p in [16w, 16w+16)
-  wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc[kN / 16];
+  const uint32_t b_tile_full = smem_u32(&bars->tile_full), b_tiles_free = smem_u32(&bars->tiles_free),
+                 b_e1a = smem_u32(&bars->e1a), b_inter_done = smem_u32(&bars->inter_done),
+                 b_e1b = smem_u32(&bars->e1b), b_g_ready = smem_u32(&bars->g_ready),
+                 b_m_ready = smem_u32(&bars->m_ready), b_y_ready = smem_u32(&bars->y_ready);
+
+  if (warp == 4) {
+    // ================================ TMA producer ================================
+    if (lane == 0) {
+      bool ok = true;
+      int issued = 0;
+      for (int s = 0; s < nsteps; ++s) {
+        if (s > 0) {
+          ok = mbar_wait(b_tiles_free, (s - 1) & 1, abort_flag);
+          if (!ok) { ssd_report(status, kErrSsdProducer, s); break; }
+        }
+        const int row = b * L + s * kQ;
+        mbar_arrive_expect_tx(b_tile_full, kTileBytes);
+        tma_load_2d(sC, &tm_c, g * kN, row, b_tile_full);
+        tma_load_2d(sC + kBCBox, &tm_c, g * kN + 64, row, b_tile_full);
+        tma_load_2d(sB, &tm_b, g * kN, row, b_tile_full);
+        tma_load_2d(sB + kBCBox, &tm_b, g * kN + 64, row, b_tile_full);
+        tma_load_2d(sX, &tm_x, h * kP, row, b_tile_full);
+        ++issued;
+      }
+      if (!ok && issued > 0) {
+        for (int spin = 0; spin < 100000; ++spin) {  // let the copies in flight land before smem goes away
+          if (mbar_try_wait(b_tile_full, (issued - 1) & 1)) break;
+          __nanosleep(100);
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 5) {
+    // ================================ MMA issuer ==================================
+    if (lane == 0) {
+      constexpr int fmt = (DT == NB200_BF16) ? 1 : 0;
+      constexpr uint32_t id_inter = umma_idesc_f16_ab(fmt, 0, 1, kQ, kP);   // A: TMEM, B: S_in [n][p] MN-major
+      constexpr uint32_t id_g = umma_idesc_f16_ab(fmt, 0, 0, kQ, kQ);       // A: C, B: B, both K-major
+      constexpr uint32_t id_z = umma_idesc_f16_ab(fmt, 1, 1, kN, kP);       // A: B^T (MN-major), B: w x (MN-major)
+      constexpr uint32_t id_m2 = umma_idesc_f16_ab(fmt, 0, 1, kQ, kP);      // A: TMEM, B: x (MN-major)
+      uint64_t dC[8], dB[8], dBt[8], dX[8], dXs[8];
 #pragma unroll
-  for (int n = 0; n < kN / 16; ++n) wmma::fill_fragment(acc[n], 0.f);
+      for (int kk = 0; kk < 8; ++kk) {
+        const uint32_t off = (kk >> 2) * kBCBox + (kk & 3) * 32;  // 16 elements of n per MMA inside the swizzled row
+        dC[kk] = umma_desc_sw128(sC + off, 16, 1024);
+        dB[kk] = umma_desc_sw128(sB + off, 16, 1024);
+        // reduction over rows (time steps / state rows): 16 rows = 2 KB per MMA; 64-column blocks 16 KB apart
+        dBt[kk] = umma_desc_sw128(sB + kk * 2048, kBCBox, 1024);
+        dX[kk] = umma_desc_sw128(sX + kk * 2048, kXBytes, 1024);
+        dXs[kk] = umma_desc_sw128(sXs + kk * 2048, kXBytes, 1024);
+      }
+      bool ok = true;
+      for (int s = 0; s < nsteps && ok; ++s) {
+        const uint32_t ph = s & 1;
+        ok = mbar_wait(b_tile_full, ph, abort_flag);
+        if (!ok) { ssd_report(status, kErrSsdMma, 4 * s); break; }
+        ok = mbar_wait(b_e1a, ph, abort_flag);
+        if (!ok) { ssd_report(status, kErrSsdMma, 4 * s + 1); break; }
+        tc_fence_after();
+        // Y = (C e^cum) . S_in      (S_in sits in the buffer that later holds w*x)
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) umma_ts(tY, tR + kk * 8, dXs[kk], id_inter, kk > 0);
+        umma_commit(b_inter_done);
+        // G = C . B^T  (overwrites the scaled C: MMAs execute in issue order)
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) umma_ss(tR, dC[kk], dB[kk], id_g, kk > 0);
+        umma_commit(b_g_ready);
+        // S = (e^cum_last S) + B^T . (w x)
+        ok = mbar_wait(b_e1b, ph, abort_flag);
+        if (!ok) { ssd_report(status, kErrSsdMma, 4 * s + 2); break; }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) umma_ss(tS, dBt[kk], dXs[kk], id_z, 1u);
+        // Y += (G o decay o mask) . x
+        ok = mbar_wait(b_m_ready, ph, abort_flag);
+        if (!ok) { ssd_report(status, kErrSsdMma, 4 * s + 3); break; }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) umma_ts(tY, tR + kk * 8, dX[kk], id_m2, 1u);
+        umma_commit(b_y_ready);
+        umma_commit(b_tiles_free);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ================================ element-wise warps ==========================
+    const int i = warp * 32 + lane;                           // row of the step == TMEM lane
+    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    float *lb = lb_all + warp * kQ;                            // this warp's copy of cum_j - log2(dt_j)
+    const float a_log2 = A[h] * kLog2e;
+    {  // the state starts at zero
+      uint32_t z[32];
+#pragma unroll
+      for (int k = 0; k < 32; ++k) z[k] = 0u;
+      tmem_st32(tS + lane_addr, z);
+      tmem_st32(tS + lane_addr + 32, z);
+      tmem_wait_st();
+    }
+    bool ok = true;
+    for (int s = 0; s < nsteps; ++s) {
+      const uint32_t ph = s & 1;
+      const size_t row0 = static_cast<size_t>(b) * L + static_cast<size_t>(s) * kQ;
 
-  for (int j0 = 0; j0 < Q; j0 += kJB) {
-    // stage: x rows are 64 elements (128 B) = 8 x 16 B; B rows are 128 elements = 16 x 16 B
-    for (int idx = tid; idx < kJB * 8; idx += 128) {
-      const int r = idx >> 3, seg = idx & 7;
-      const uint4 w = *reinterpret_cast<const uint4 *>(x + ((t0 + j0 + r) * H + h) * kP + seg * 8);
-      const float wj = sW[j0 + r];
-      const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
-      uint4 o;
-      uint32_t *os = reinterpret_cast<uint32_t *>(&o);
+      // ---- prefix sum of dt*A over the 128 rows, every warp for itself: lane l holds rows 4l..4l+3 ----
+      float dt4[4], cum4[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) dt4[e] = dt[(row0 + 4 * lane + e) * H + h];
+      cum4[0] = dt4[0] * a_log2;
+#pragma unroll
+      for (int e = 1; e < 4; ++e) cum4[e] = cum4[e - 1] + dt4[e] * a_log2;
+      float incl = cum4[3];
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const float o = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += o;
+      }
+      const float excl = incl - cum4[3];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) cum4[e] += excl;
+      const float total = __shfl_sync(0xffffffffu, cum4[3], 31);
+      __syncwarp();  // the previous step's readers of lb are done
+      *reinterpret_cast<float4 *>(lb + 4 * lane) =
+          make_float4(cum4[0] - lg2(dt4[0]), cum4[1] - lg2(dt4[1]), cum4[2] - lg2(dt4[2]), cum4[3] - lg2(dt4[3]));
+      __syncwarp();
+      // this thread's own row: lane (i mod 32) / 4 ... of this warp's block of 32 rows lives at lane 8*warp + lane/4
+      const int src = 8 * warp + (lane >> 2), comp = lane & 3;
+      float cum_i = 0.f, dt_i = 0.f;
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const float2 f = unpack2<DT>(ws[e]);
-        os[e] = pack2<DT>(f.x * wj, f.y * wj);
+        const float cv = __shfl_sync(0xffffffffu, cum4[e], src), dv = __shfl_sync(0xffffffffu, dt4[e], src);
+        if (comp == e) { cum_i = cv; dt_i = dv; }
       }
-      *reinterpret_cast<uint4 *>(sXs + r * kLdP + seg * 8) = o;
-    }
-    for (int idx = tid; idx < kJB * 16; idx += 128) {
-      const int r = idx >> 4, seg = idx & 15;
-      *reinterpret_cast<uint4 *>(sB + r * kLdN + seg * 8) =
-          *reinterpret_cast<const uint4 *>(Bm + ((t0 + j0 + r) * G + g) * kN + seg * 8);
-    }
-    __syncthreads();
+
+      ok = __all_sync(0xffffffffu, mbar_wait(b_tile_full, ph, abort_flag));
+      if (!ok) { ssd_report(status, kErrSsdCompute, 8 * s); break; }
+
+      // ---- E1a: C_i e^cum_i -> TMEM columns 0..63 (16 bit); S_in -> 16 bit in smem; S *= e^cum_last ----
+      {
+        const float ei = ex2(cum_i);
 #pragma unroll
-    for (int k = 0; k < kJB / 16; ++k) {
-      wmma::fragment<wmma::matrix_a, 16, 16, 16, T, wmma::col_major> fa;   // A[p][j] = Xs[j][p]
-      wmma::load_matrix_sync(fa, sXs + (k * 16) * kLdP + warp * 16, kLdP);
+        for (int q4 = 0; q4 < 4; ++q4) {
+          uint32_t pk[16];
 #pragma unroll
-      for (int n = 0; n < kN / 16; ++n) {
-        wmma::fragment<wmma::matrix_b, 16, 16, 16, T, wmma::row_major> fb;  // B[j][n]
-        wmma::load_matrix_sync(fb, sB + (k * 16) * kLdN + n * 16, kLdN);
-        wmma::mma_sync(acc[n], fa, fb, acc[n]);
+          for (int cc = 0; cc < 4; ++cc) {
+            const int c = q4 * 4 + cc;  // 16-byte chunk of the 256-byte row; two boxes of eight chunks
+            const uint4 w = *reinterpret_cast<const uint4 *>(pC + (c >> 3) * kBCBox + sw128(i, c & 7));
+            const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 f = unpack2<DT>(ws[e]);
+              pk[cc * 4 + e] = pack2<DT>(f.x * ei, f.y * ei);
+            }
+          }
+          tmem_st16(tR + lane_addr + q4 * 16, pk);
+        }
+        uint32_t sv[kP];
+        tmem_ld32p(tS + lane_addr, sv);
+        tmem_ld32p(tS + lane_addr + 32, sv + 32);
+        tmem_wait_ld();
+        const float et = ex2(total);
+#pragma unroll
+        for (int cc = 0; cc < 8; ++cc) {
+          uint4 w;
+          w.x = pack2<DT>(__uint_as_float(sv[8 * cc + 0]), __uint_as_float(sv[8 * cc + 1]));
+          w.y = pack2<DT>(__uint_as_float(sv[8 * cc + 2]), __uint_as_float(sv[8 * cc + 3]));
+          w.z = pack2<DT>(__uint_as_float(sv[8 * cc + 4]), __uint_as_float(sv[8 * cc + 5]));
+          w.w = pack2<DT>(__uint_as_float(sv[8 * cc + 6]), __uint_as_float(sv[8 * cc + 7]));
+          *reinterpret_cast<uint4 *>(pXs + sw128(i, cc)) = w;
+        }
+#pragma unroll
+        for (int k = 0; k < kP; ++k) sv[k] = __float_as_uint(__uint_as_float(sv[k]) * et);
+        tmem_st32(tS + lane_addr, *reinterpret_cast<uint32_t(*)[32]>(sv));
+        tmem_st32(tS + lane_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(sv + 32));
+        tmem_wait_st();
+        tc_fence_before();
+        fence_proxy_async_smem();   // the tensor core reads shared memory through the async proxy
+        mbar_arrive(b_e1a);
       }
-    }
-    __syncthreads();
-  }
-  float *z = state_ws + ((((size_t)b * H + h) * nc + c) * kP + warp * 16) * kN;
+
+      // ---- E1b: w_i x_i -> smem (the buffer S_in occupied, free once the first product has retired) ----
+      ok = __all_sync(0xffffffffu, mbar_wait(b_inter_done, ph, abort_flag));
+      if (!ok) { ssd_report(status, kErrSsdCompute, 8 * s + 1); break; }
+      {
+        const float wi = ex2(total - cum_i) * dt_i;
 #pragma unroll
-  for (int n = 0; n < kN / 16; ++n) wmma::store_matrix_sync(z + n * 16, acc[n], kN, wmma::mem_row_major);
-}
+        for (int cc = 0; cc < 8; ++cc) {
+          const uint4 w = *reinterpret_cast<const uint4 *>(pX + sw128(i, cc));
+          const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+          uint4 o;
+          uint32_t *os = reinterpret_cast<uint32_t *>(&o);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 f = unpack2<DT>(ws[e]);
+            os[e] = pack2<DT>(f.x * wi, f.y * wi);
+          }
+          *reinterpret_cast<uint4 *>(pXs + sw128(i, cc)) = o;
+        }
+        fence_proxy_async_smem();
+        mbar_arrive(b_e1b);
+      }
 
-// ---- kernel 2: fp32 state recurrence across chunks, in place ------------------------------------
-__global__ void __launch_bounds__(256)
-ssd_state_pass_kernel(const float *__restrict__ cum_ws, float *__restrict__ state_ws, int nc, int Q) {
-  const size_t bh = blockIdx.y;
-  const int e = blockIdx.x * 256 + threadIdx.x;  // element of the P x N state
-  float s = 0.f;
-  for (int c = 0; c < nc; ++c) {
-    float *p = state_ws + (bh * nc + c) * (size_t)(kP * kN) + e;
-    const float z = *p;
-    *p = s;  // state entering chunk c
-    const float decay = ex2(cum_ws[(bh * nc + c) * Q + (Q - 1)] * kLog2e);
-    s = fmaf(decay, s, z);
-  }
-}
+      // ---- E2: G_ij e^(cum_i - cum_j) dt_j for j <= i, else 0 -> 16 bit over G in place ----
+      ok = __all_sync(0xffffffffu, mbar_wait(b_g_ready, ph, abort_flag));
+      if (!ok) { ssd_report(status, kErrSsdCompute, 8 * s + 2); break; }
+      tc_fence_after();
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t pk[16];
+        if (c <= warp) {  // warp-uniform: columns beyond this warp's last row are masked for all its rows
+          uint32_t gv[32];
+          tmem_ld32(tR + lane_addr + c * 32, gv);
+          tmem_wait_ld();
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const float4 l4 = *reinterpret_cast<const float4 *>(lb + c * 32 + q * 4);
+            const float lbs[4] = {l4.x, l4.y, l4.z, l4.w};
+            float m[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int j = c * 32 + q * 4 + e;
+              const float val = __uint_as_float(gv[q * 4 + e]) * ex2(cum_i - lbs[e]);
+              m[e] = (j <= i) ? val : 0.f;
+            }
+            pk[q * 2] = pack2<DT>(m[0], m[1]);
+            pk[q * 2 + 1] = pack2<DT>(m[2], m[3]);
+          }
+        } else {
+#pragma unroll
+          for (int k = 0; k < 16; ++k) pk[k] = 0u;
+        }
+        tmem_st16(tR + lane_addr + c * 16, pk);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(b_m_ready);
 
-// ---- kernel 3: outputs ---------------------------------------------------------------------------
-template <int DT>
-__global__ void __launch_bounds__(128)
-ssd_chunk_scan_kernel(const uint16_t *__restrict__ x, const float *__restrict__ dt, const uint16_t *__restrict__ Bm,
-                      const uint16_t *__restrict__ Cm, const float *__restrict__ cum_ws,
-                      const float *__restrict__ state_ws, uint16_t *__restrict__ y, int L, int H, int G, int Q) {
-  using T = typename WmmaElem<DT>::type;
-  extern __shared__ __align__(128) unsigned char smem_raw[];
-  T *sC = reinterpret_cast<T *>(smem_raw);          // [64][kLdN]  C rows of this block
-  T *sB = sC + kJB * kLdN;                          // [64][kLdN]  B rows of block j
-  T *sS = sB + kJB * kLdN;                          // [64 p][kLdN] entering state, rounded
-  T *sX = sS + kP * kLdN;                           // [64][kLdP]  x rows of block j
-  T *sM = sX + kJB * kLdP;                          // [64][kLdP]  masked, decayed C.B^T
-  float *sG = reinterpret_cast<float *>(sM + kJB * kLdP);  // [64][kLdG] fp32 scratch
-  float *sCumI = sG + kJB * kLdG;                   // [64]
-  float *sCumJ = sCumI + kJB;                       // [64]
-  float *sDtJ = sCumJ + kJB;                        // [64]
-
-  const int nib = Q / kJB;
-  const int ib = blockIdx.x % nib, h = blockIdx.x / nib, c = blockIdx.y, b = blockIdx.z;
-  const int nc = L / Q;
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int g = h / (H / G);
-  const size_t t0 = (size_t)b * L + (size_t)c * Q;
-  const size_t bhc = ((size_t)b * H + h) * nc + c;
-  const float *cum = cum_ws + bhc * Q;
-  const int i0 = ib * kJB;
-
-  for (int idx = tid; idx < kJB * 16; idx += 128) {
-    const int r = idx >> 4, seg = idx & 15;
-    *reinterpret_cast<uint4 *>(sC + r * kLdN + seg * 8) =
-        *reinterpret_cast<const uint4 *>(Cm + ((t0 + i0 + r) * G + g) * kN + seg * 8);
-  }
-  {
-    const float *st = state_ws + bhc * (size_t)(kP * kN);
-    for (int idx = tid; idx < kP * kN / 4; idx += 128) {
-      const int p = idx / (kN / 4), q = idx % (kN / 4);
-      const float4 f = *reinterpret_cast<const float4 *>(st + p * kN + q * 4);
-      uint2 w;
-      w.x = pack2<DT>(f.x, f.y);
-      w.y = pack2<DT>(f.z, f.w);
-      *reinterpret_cast<uint2 *>(sS + p * kLdN + q * 4) = w;
+      // ---- E3: Y -> storage dtype -> global (one 128-byte row per thread) ----
+      ok = __all_sync(0xffffffffu, mbar_wait(b_y_ready, ph, abort_flag));
+      if (!ok) { ssd_report(status, kErrSsdCompute, 8 * s + 3); break; }
+      tc_fence_after();
+      {
+        uint32_t yv[kP];
+        tmem_ld32p(tY + lane_addr, yv);
+        tmem_ld32p(tY + lane_addr + 32, yv + 32);
+        tmem_wait_ld();
+        uint16_t *dst = y + ((row0 + i) * H + h) * kP;
+#pragma unroll
+        for (int cc = 0; cc < 8; ++cc) {
+          uint4 w;
+          w.x = pack2<DT>(__uint_as_float(yv[8 * cc + 0]), __uint_as_float(yv[8 * cc + 1]));
+          w.y = pack2<DT>(__uint_as_float(yv[8 * cc + 2]), __uint_as_float(yv[8 * cc + 3]));
+          w.z = pack2<DT>(__uint_as_float(yv[8 * cc + 4]), __uint_as_float(yv[8 * cc + 5]));
+          w.w = pack2<DT>(__uint_as_float(yv[8 * cc + 6]), __uint_as_float(yv[8 * cc + 7]));
+          *reinterpret_cast<uint4 *>(dst + cc * 8) = w;
+        }
+      }
+      tc_fence_before();  // orders these TMEM reads before the next step's products, via the e1a arrival
     }
   }
-  if (tid < kJB) sCumI[tid] = cum[i0 + tid];
+
+  // ================================ tear-down =====================================
+  tc_fence_before();
   __syncthreads();
-
-  // inter-chunk term: Y = e^(cum_i) * (C_i . S_in^T); warp w owns rows [16w, 16w+16)
-  wmma::fragment<wmma::accumulator, 16, 16, 16, float> yacc[kP / 16];
-#pragma unroll
-  for (int n = 0; n < kP / 16; ++n) wmma::fill_fragment(yacc[n], 0.f);
-#pragma unroll
-  for (int k = 0; k < kN / 16; ++k) {
-    wmma::fragment<wmma::matrix_a, 16, 16, 16, T, wmma::row_major> fa;
-    wmma::load_matrix_sync(fa, sC + (warp * 16) * kLdN + k * 16, kLdN);
-#pragma unroll
-    for (int n = 0; n < kP / 16; ++n) {
-      wmma::fragment<wmma::matrix_b, 16, 16, 16, T, wmma::col_major> fb;  // B[k=n_state][p] = S[p][n_state]
-      wmma::load_matrix_sync(fb, sS + (n * 16) * kLdN + k * 16, kLdN);
-      wmma::mma_sync(yacc[n], fa, fb, yacc[n]);
-    }
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem, kSsdTmemCols);
   }
-  float *gw = sG + (warp * 16) * kLdG;  // this warp's 16 rows of scratch
-#pragma unroll
-  for (int n = 0; n < kP / 16; ++n) wmma::store_matrix_sync(gw + n * 16, yacc[n], kLdG, wmma::mem_row_major);
-  __syncwarp();
-  for (int e = lane; e < 16 * kP; e += 32) {
-    const int r = e / kP, col = e % kP;
-    gw[r * kLdG + col] *= ex2(sCumI[warp * 16 + r] * kLog2e);
-  }
-  __syncwarp();
-#pragma unroll
-  for (int n = 0; n < kP / 16; ++n) wmma::load_matrix_sync(yacc[n], gw + n * 16, kLdG, wmma::mem_row_major);
-
-  // intra-chunk term over the blocks j <= i
-  for (int jb = 0; jb <= ib; ++jb) {
-    const int j0 = jb * kJB;
-    __syncthreads();  // previous block's sB / sX fully consumed
-    for (int idx = tid; idx < kJB * 16; idx += 128) {
-      const int r = idx >> 4, seg = idx & 15;
-      *reinterpret_cast<uint4 *>(sB + r * kLdN + seg * 8) =
-          *reinterpret_cast<const uint4 *>(Bm + ((t0 + j0 + r) * G + g) * kN + seg * 8);
-    }
-    for (int idx = tid; idx < kJB * 8; idx += 128) {
-      const int r = idx >> 3, seg = idx & 7;
-      *reinterpret_cast<uint4 *>(sX + r * kLdP + seg * 8) =
-          *reinterpret_cast<const uint4 *>(x + ((t0 + j0 + r) * H + h) * kP + seg * 8);
-    }
-    if (tid < kJB) {
-      sCumJ[tid] = cum[j0 + tid];
-      sDtJ[tid] = dt[(t0 + j0 + tid) * H + h];
-    }
-    __syncthreads();
-
-    // G = C_i . B_j^T  (16 rows of this warp x 64 columns)
-    wmma::fragment<wmma::accumulator, 16, 16, 16, float> gacc[kJB / 16];
-#pragma unroll
-    for (int n = 0; n < kJB / 16; ++n) wmma::fill_fragment(gacc[n], 0.f);
-#pragma unroll
-    for (int k = 0; k < kN / 16; ++k) {
-      wmma::fragment<wmma::matrix_a, 16, 16, 16, T, wmma::row_major> fa;
-      wmma::load_matrix_sync(fa, sC + (warp * 16) * kLdN + k * 16, kLdN);
-#pragma unroll
-      for (int n = 0; n < kJB / 16; ++n) {
-        wmma::fragment<wmma::matrix_b, 16, 16, 16, T, wmma::col_major> fb;  // B[k][j] = Bm[j][k]
-        wmma::load_matrix_sync(fb, sB + (n * 16) * kLdN + k * 16, kLdN);
-        wmma::mma_sync(gacc[n], fa, fb, gacc[n]);
-      }
-    }
-#pragma unroll
-    for (int n = 0; n < kJB / 16; ++n) wmma::store_matrix_sync(gw + n * 16, gacc[n], kLdG, wmma::mem_row_major);
-    __syncwarp();
-    // M = G * e^(cum_i - cum_j) * dt_j for j <= i, else 0; rounded to the storage dtype
-    T *mw = sM + (warp * 16) * kLdP;
-    for (int e = lane; e < 16 * kJB; e += 32) {
-      const int r = e / kJB, col = e % kJB;
-      const int gi = i0 + warp * 16 + r, gj = j0 + col;
-      float m = 0.f;
-      if (gj <= gi) m = gw[r * kLdG + col] * ex2((sCumI[warp * 16 + r] - sCumJ[col]) * kLog2e) * sDtJ[col];
-      mw[r * kLdP + col] = to_elem<DT>(m);
-    }
-    __syncwarp();
-    // Y += M . X_j
-#pragma unroll
-    for (int k = 0; k < kJB / 16; ++k) {
-      wmma::fragment<wmma::matrix_a, 16, 16, 16, T, wmma::row_major> fa;
-      wmma::load_matrix_sync(fa, mw + k * 16, kLdP);
-#pragma unroll
-      for (int n = 0; n < kP / 16; ++n) {
-        wmma::fragment<wmma::matrix_b, 16, 16, 16, T, wmma::row_major> fb;  // X[j][p]
-        wmma::load_matrix_sync(fb, sX + (k * 16) * kLdP + n * 16, kLdP);
-        wmma::mma_sync(yacc[n], fa, fb, yacc[n]);
-      }
-    }
-  }
-
-  // y rows -> storage dtype -> global (rows are 64 elements = 128 bytes)
-#pragma unroll
-  for (int n = 0; n < kP / 16; ++n) wmma::store_matrix_sync(gw + n * 16, yacc[n], kLdG, wmma::mem_row_major);
-  __syncwarp();
-  for (int e = lane; e < 16 * (kP / 8); e += 32) {
-    const int r = e / (kP / 8), seg = e % (kP / 8);
-    const float *src = gw + r * kLdG + seg * 8;
-    uint4 w;
-    w.x = pack2<DT>(src[0], src[1]);
-    w.y = pack2<DT>(src[2], src[3]);
-    w.z = pack2<DT>(src[4], src[5]);
-    w.w = pack2<DT>(src[6], src[7]);
-    *reinterpret_cast<uint4 *>(y + ((t0 + i0 + warp * 16 + r) * H + h) * kP + seg * 8) = w;
-  }
-}
-
-size_t k1_smem(int Q) { return (size_t)(kJB * kLdP + kJB * kLdN) * 2 + (size_t)2 * Q * sizeof(float); }
-size_t k3_smem() {
-  return (size_t)(2 * kJB * kLdN + kP * kLdN + 2 * kJB * kLdP) * 2 + (size_t)(kJB * kLdG + 3 * kJB) * sizeof(float);
 }
 
 template <int DT>
-int launch_ssd(const void *x, const float *dt, const float *A, const void *Bm, const void *Cm, void *y,
-               void *workspace, int B, int L, int H, int G, int Q, cudaStream_t st) {
-  const int nc = L / Q;
-  float *cum_ws = static_cast<float *>(workspace);
-  float *state_ws = cum_ws + (size_t)B * H * nc * Q;
-  const auto *xp = static_cast<const uint16_t *>(x);
-  const auto *bp = static_cast<const uint16_t *>(Bm);
-  const auto *cp = static_cast<const uint16_t *>(Cm);
-  NB200_CHECK_CUDA(cudaFuncSetAttribute(ssd_chunk_scan_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        (int)k3_smem()));
-  ssd_chunk_state_kernel<DT><<<dim3(H, nc, B), 128, k1_smem(Q), st>>>(xp, dt, A, bp, cum_ws, state_ws, L, H, G, Q);
-  NB200_CHECK_CUDA(cudaGetLastError());
-  ssd_state_pass_kernel<<<dim3(kP * kN / 256, B * H), 256, 0, st>>>(cum_ws, state_ws, nc, Q);
-  NB200_CHECK_CUDA(cudaGetLastError());
-  ssd_chunk_scan_kernel<DT><<<dim3(H * (Q / kJB), nc, B), 128, k3_smem(), st>>>(
-      xp, dt, bp, cp, cum_ws, state_ws, static_cast<uint16_t *>(y), L, H, G, Q);
+int launch_ssd(const void *x, const float *dt, const float *A, const void *Bm, const void *Cm, void *y, int B, int L,
+               int H, int G, int dtype, int *status, cudaStream_t st) {
+  CUtensorMap tx, tb, tc;
+  int rc;
+  if ((rc = tma_map_2d_sw128(&tx, x, (long long)B * L, (long long)H * kP, dtype, kQ, "ssd_chunk_scan")) != NB200_OK) return rc;
+  if ((rc = tma_map_2d_sw128(&tb, Bm, (long long)B * L, (long long)G * kN, dtype, kQ, "ssd_chunk_scan")) != NB200_OK) return rc;
+  if ((rc = tma_map_2d_sw128(&tc, Cm, (long long)B * L, (long long)G * kN, dtype, kQ, "ssd_chunk_scan")) != NB200_OK) return rc;
+  NB200_CHECK_CUDA(cudaFuncSetAttribute(ssd_fused_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSsdSmem));
+  NB200_CHECK_CUDA(cudaFuncSetAttribute(ssd_fused_kernel<DT>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                        cudaSharedmemCarveoutMaxShared));
+  ssd_fused_kernel<DT><<<dim3(B * H), dim3(kSsdThreads), kSsdSmem, st>>>(tx, tb, tc, dt, A, static_cast<uint16_t *>(y),
+                                                                         L, H, G, status);
   NB200_CHECK_CUDA(cudaGetLastError());
   return NB200_OK;
 }
 
 bool ssd_shape_ok(int B, int L, int H, int P, int N, int G, int chunk) {
   return B > 0 && L > 0 && H > 0 && G > 0 && P == kP && N == kN && H % G == 0 &&
-         (chunk == 64 || chunk == 128 || chunk == 256) && L % chunk == 0;
+         (chunk == 64 || chunk == 128 || chunk == 256) && L % kQ == 0 && L % chunk == 0;
 }
 
 }  // namespace
@@ -334,8 +425,7 @@ using namespace nb200;
 
 extern "C" size_t nb200_ssd_workspace_bytes(int B, int L, int H, int P, int N, int G, int chunk) {
   if (!ssd_shape_ok(B, L, H, P, N, G, chunk)) return 0;
-  const size_t nc = L / chunk;
-  return (size_t)B * H * nc * ((size_t)chunk + (size_t)P * N) * sizeof(float);
+  return NB200_STATUS_WORDS * sizeof(int);  // the state stays on chip; only the status words live here
 }
 
 extern "C" int nb200_ssd_chunk_scan_fwd(const void *x, const float *dt, const float *A, const void *Bm,
@@ -344,13 +434,15 @@ extern "C" int nb200_ssd_chunk_scan_fwd(const void *x, const float *dt, const fl
   NB200_REQUIRE(x && dt && A && Bm && Cm && y && workspace, NB200_ERR_BAD_ARG, "ssd_chunk_scan: null pointer");
   NB200_REQUIRE(B > 0 && L > 0 && H > 0 && G > 0, NB200_ERR_BAD_ARG, "ssd_chunk_scan: non-positive extent");
   NB200_REQUIRE(ssd_shape_ok(B, L, H, P, N, G, chunk), NB200_ERR_UNSUPPORTED,
-                "ssd_chunk_scan: need P == 64, N == 128, H %% G == 0, chunk in {64,128,256}, L %% chunk == 0");
-  NB200_REQUIRE(aligned16(x) && aligned16(Bm) && aligned16(Cm) && aligned16(y) &&
-                    (reinterpret_cast<uintptr_t>(workspace) & 31u) == 0,
-                NB200_ERR_BAD_ARG, "ssd_chunk_scan: tensors must be 16-byte and the workspace 32-byte aligned");
-  NB200_REQUIRE(B <= 65535 && L / chunk <= 65535, NB200_ERR_UNSUPPORTED, "ssd_chunk_scan: grid too large");
+                "ssd_chunk_scan: need P == 64, N == 128, H %% G == 0, chunk in {64,128,256}, L a multiple of 128 and of chunk");
+  NB200_REQUIRE(aligned16(x) && aligned16(Bm) && aligned16(Cm) && aligned16(y) && aligned16(workspace),
+                NB200_ERR_BAD_ARG, "ssd_chunk_scan: tensors and workspace must be 16-byte aligned");
+  NB200_REQUIRE((long long)B * L < (1ll << 31) && (long long)B * H < (1ll << 31), NB200_ERR_UNSUPPORTED,
+                "ssd_chunk_scan: problem too large");
   auto st = static_cast<cudaStream_t>(stream);
-  if (dtype == NB200_BF16) return launch_ssd<NB200_BF16>(x, dt, A, Bm, Cm, y, workspace, B, L, H, G, chunk, st);
-  if (dtype == NB200_F16) return launch_ssd<NB200_F16>(x, dt, A, Bm, Cm, y, workspace, B, L, H, G, chunk, st);
+  int *status = static_cast<int *>(workspace);
+  NB200_CHECK_CUDA(cudaMemsetAsync(status, 0, NB200_STATUS_WORDS * sizeof(int), st));
+  if (dtype == NB200_BF16) return launch_ssd<NB200_BF16>(x, dt, A, Bm, Cm, y, B, L, H, G, dtype, status, st);
+  if (dtype == NB200_F16) return launch_ssd<NB200_F16>(x, dt, A, Bm, Cm, y, B, L, H, G, dtype, status, st);
   return fail(NB200_ERR_UNSUPPORTED, "ssd_chunk_scan: dtype %d (f16 and bf16 only)", dtype);
 }

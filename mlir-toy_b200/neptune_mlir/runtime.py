@@ -142,6 +142,13 @@ def selective_scan(u, delta, A, Bm, Cm, Dskip, z, out, *, B, Dm, L, N, dtype) ->
     native.check(rc, "nb200_selective_scan_fwd")
 
 
+def check_workspace_status(workspace) -> None:
+    """Synchronise and raise if the SSD kernel recorded an expired device-side wait in ``workspace``."""
+    dev = workspace.device
+    rc = native.lib().nb200_status_read(workspace.data_ptr(), None, _stream(dev))
+    native.check(rc, "nb200 ssd status")
+
+
 def ssd_workspace_bytes(B, L, H, P, N, G, chunk) -> int:
     return native.lib().nb200_ssd_workspace_bytes(B, L, H, P, N, G, chunk)
 

@@ -146,6 +146,7 @@ def test_ssd_small(cuda, native_lib, chunk, G):
     y = torch.full((B, L, H, P), float("nan"), dtype=torch.bfloat16, device=cuda)
     mod.ssd_small(x.to(cuda), dt.to(cuda), A.to(cuda), Bm.to(cuda), Cm.to(cuda), ws, y)
     finish()
+    runtime.check_workspace_status(ws)
     ref = ssd.ssd_reference(x, dt, A, Bm, Cm)
     assert_storage_close(y, ref, BF16_ATOL, 2 * BF16_ULP, scale_by_rms=True)
     assert_rms_close(y, ref, 2.0 ** -8)
@@ -165,6 +166,7 @@ def test_ssd_config5_full_size_sampled(cuda, native_lib):
     y = torch.full((B, L, H, P), float("nan"), dtype=torch.bfloat16, device=cuda)
     mod.ssd_chunk_scan_bf16(x, dt, A, Bm, Cm, ws, y)
     finish()
+    runtime.check_workspace_status(ws)
     assert bool(torch.isfinite(y).all())
     heads = [0, 63]
     ref = ssd.ssd_reference(x[:1, :, heads].cpu(), dt[:1, :, heads].cpu(), A[heads].cpu(), Bm[:1].cpu(), Cm[:1].cpu())

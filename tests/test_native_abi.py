@@ -71,7 +71,7 @@ def test_version_and_argument_errors_without_a_gpu(native_lib):
 def test_workspace_sizes(native_lib):
     lib = native.load(str(native_lib))
     assert lib.nb200_decode_workspace_bytes(64, 32, 128, 16) == 64 * 32 * 16 * 130 * 4
-    assert lib.nb200_ssd_workspace_bytes(4, 8192, 64, 64, 128, 1, 256) == 4 * 64 * 32 * (256 + 64 * 128) * 4
+    assert lib.nb200_ssd_workspace_bytes(4, 8192, 64, 64, 128, 1, 256) == 16
     assert lib.nb200_ssd_workspace_bytes(4, 8192, 64, 32, 128, 1, 256) == 0
 
 
