@@ -18,7 +18,9 @@
 //   warps 0-3   thread i = row i of the step = TMEM lane i: prefix sum of dt*A (each warp scans all
 //               128 values itself, so no cross-warp exchange), the scaled copies of C, x and S, the
 //               decay/mask pass over G, and the epilogue (Y -> 16 bit -> global)
-//   warp 4      TMA producer: B, C (two 64-column boxes each) and x tiles of the next step
+//   warp 4      TMA producer: the C, B and x tiles of the next step, each issued as soon as the
+//               product that last read its buffer has retired, and the TMA store of the finished
+//               Y tile (staged by the element-wise warps in the buffer x occupied)
 //   warp 5      MMA issuer, operand descriptors built once
 //
 // All exponents are <= 0 (A < 0), so nothing overflows.  TMEM: columns 0-127 hold C e^cum, then G,
@@ -50,7 +52,7 @@ constexpr float kLog2e = 1.4426950408889634f;
 enum : int { kErrSsdProducer = 11, kErrSsdMma = 12, kErrSsdCompute = 13, kErrSsdAlign = 15 };
 
 struct SsdBarriers {
-  uint64_t tile_full, tiles_free, e1a, inter_done, e1b, g_ready, m_ready, y_ready;
+  uint64_t c_full, b_full, x_full, z_done, y_staged, e1a, inter_done, e1b, g_ready, m_ready, y_ready;
   uint32_t tmem_base;
   int abort_flag;
   int skip;
@@ -76,7 +78,7 @@ __device__ __forceinline__ uint32_t sw128(int r, int c) { return r * 128 + ((c ^
 template <int DT>
 __global__ void __launch_bounds__(kSsdThreads, 2)
 ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_b,
-                 const __grid_constant__ CUtensorMap tm_c, const float *__restrict__ dt, const float *__restrict__ A,
+                 const __grid_constant__ CUtensorMap tm_c, const __grid_constant__ CUtensorMap tm_y, const float *__restrict__ dt, const float *__restrict__ A,
                  uint16_t *__restrict__ y, int L, int H, int G, int *status) {
   extern __shared__ __align__(1024) unsigned char smem[];
   const uint32_t base = smem_u32(smem);
@@ -98,8 +100,11 @@ ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
   if (threadIdx.x == 0) {
     bars->abort_flag = 0;
     bars->skip = (status != nullptr && *reinterpret_cast<volatile int *>(status) != 0) ? 1 : 0;
-    mbar_init(smem_u32(&bars->tile_full), 1);
-    mbar_init(smem_u32(&bars->tiles_free), 1);
+    mbar_init(smem_u32(&bars->c_full), 1);
+    mbar_init(smem_u32(&bars->b_full), 1);
+    mbar_init(smem_u32(&bars->x_full), 1);
+    mbar_init(smem_u32(&bars->z_done), 1);
+    mbar_init(smem_u32(&bars->y_staged), 128);
     mbar_init(smem_u32(&bars->e1a), 128);
     mbar_init(smem_u32(&bars->inter_done), 1);
     mbar_init(smem_u32(&bars->e1b), 128);
@@ -120,6 +125,7 @@ ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
     tma_prefetch_desc(&tm_x);
     tma_prefetch_desc(&tm_b);
     tma_prefetch_desc(&tm_c);
+    tma_prefetch_desc(&tm_y);
   }
   tc_fence_before();
   __syncthreads();
@@ -127,8 +133,9 @@ ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
   const uint32_t tmem = bars->tmem_base;
   const uint32_t tR = tmem, tY = tmem + 128, tS = tmem + 192;
 
-  const uint32_t b_tile_full = smem_u32(&bars->tile_full), b_tiles_free = smem_u32(&bars->tiles_free),
-                 b_e1a = smem_u32(&bars->e1a), b_inter_done = smem_u32(&bars->inter_done),
+  const uint32_t b_c_full = smem_u32(&bars->c_full), b_b_full = smem_u32(&bars->b_full),
+                 b_x_full = smem_u32(&bars->x_full), b_z_done = smem_u32(&bars->z_done),
+                 b_y_staged = smem_u32(&bars->y_staged), b_e1a = smem_u32(&bars->e1a), b_inter_done = smem_u32(&bars->inter_done),
                  b_e1b = smem_u32(&bars->e1b), b_g_ready = smem_u32(&bars->g_ready),
                  b_m_ready = smem_u32(&bars->m_ready), b_y_ready = smem_u32(&bars->y_ready);
 
@@ -136,24 +143,58 @@ ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
     // ================================ TMA producer ================================
     if (lane == 0) {
       bool ok = true;
-      int issued = 0;
-      for (int s = 0; s < nsteps; ++s) {
-        if (s > 0) {
-          ok = mbar_wait(b_tiles_free, (s - 1) & 1, abort_flag);
-          if (!ok) { ssd_report(status, kErrSsdProducer, s); break; }
-        }
+      int issued_c = 0, issued_b = 0, issued_x = 0;
+      auto load_c = [&](int s) {
         const int row = b * L + s * kQ;
-        mbar_arrive_expect_tx(b_tile_full, kTileBytes);
-        tma_load_2d(sC, &tm_c, g * kN, row, b_tile_full);
-        tma_load_2d(sC + kBCBox, &tm_c, g * kN + 64, row, b_tile_full);
-        tma_load_2d(sB, &tm_b, g * kN, row, b_tile_full);
-        tma_load_2d(sB + kBCBox, &tm_b, g * kN + 64, row, b_tile_full);
-        tma_load_2d(sX, &tm_x, h * kP, row, b_tile_full);
-        ++issued;
+        mbar_arrive_expect_tx(b_c_full, kBCBytes);
+        tma_load_2d(sC, &tm_c, g * kN, row, b_c_full);
+        tma_load_2d(sC + kBCBox, &tm_c, g * kN + 64, row, b_c_full);
+        ++issued_c;
+      };
+      auto load_b = [&](int s) {
+        const int row = b * L + s * kQ;
+        mbar_arrive_expect_tx(b_b_full, kBCBytes);
+        tma_load_2d(sB, &tm_b, g * kN, row, b_b_full);
+        tma_load_2d(sB + kBCBox, &tm_b, g * kN + 64, row, b_b_full);
+        ++issued_b;
+      };
+      auto load_x = [&](int s) {
+        mbar_arrive_expect_tx(b_x_full, kXBytes);
+        tma_load_2d(sX, &tm_x, h * kP, b * L + s * kQ, b_x_full);
+        ++issued_x;
+      };
+      load_c(0);
+      load_b(0);
+      load_x(0);
+      for (int s = 0; s < nsteps; ++s) {
+        const uint32_t ph = s & 1;
+        const bool more = s + 1 < nsteps;
+        // the buffers of step s become free in this order: C (after G), B (after the state update), x (after Y)
+        if (more) {
+          ok = mbar_wait(b_g_ready, ph, abort_flag);
+          if (!ok) { ssd_report(status, kErrSsdProducer, 4 * s); break; }
+          load_c(s + 1);
+          ok = mbar_wait(b_z_done, ph, abort_flag);
+          if (!ok) { ssd_report(status, kErrSsdProducer, 4 * s + 1); break; }
+          load_b(s + 1);
+        }
+        // the finished Y tile sits where x was: store it, then refill the buffer with the next x
+        ok = mbar_wait(b_y_staged, ph, abort_flag);
+        if (!ok) { ssd_report(status, kErrSsdProducer, 4 * s + 2); break; }
+        tma_store_2d(&tm_y, sX, h * kP, b * L + s * kQ);
+        tma_store_commit();
+        if (more) {
+          tma_store_wait_read();
+          load_x(s + 1);
+        }
       }
-      if (!ok && issued > 0) {
-        for (int spin = 0; spin < 100000; ++spin) {  // let the copies in flight land before smem goes away
-          if (mbar_try_wait(b_tile_full, (issued - 1) & 1)) break;
+      tma_store_wait_all();
+      if (!ok) {
+        for (int spin = 0; spin < 100000; ++spin) {  // let the loads in flight land before smem goes away
+          const bool c_ok = issued_c == 0 || mbar_try_wait(b_c_full, (issued_c - 1) & 1);
+          const bool b_ok = issued_b == 0 || mbar_try_wait(b_b_full, (issued_b - 1) & 1);
+          const bool x_ok = issued_x == 0 || mbar_try_wait(b_x_full, (issued_x - 1) & 1);
+          if (c_ok && b_ok && x_ok) break;
           __nanosleep(100);
         }
       }
@@ -181,7 +222,7 @@ ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       bool ok = true;
       for (int s = 0; s < nsteps && ok; ++s) {
         const uint32_t ph = s & 1;
-        ok = mbar_wait(b_tile_full, ph, abort_flag);
+        ok = mbar_wait(b_c_full, ph, abort_flag) && mbar_wait(b_b_full, ph, abort_flag);
         if (!ok) { ssd_report(status, kErrSsdMma, 4 * s); break; }
         ok = mbar_wait(b_e1a, ph, abort_flag);
         if (!ok) { ssd_report(status, kErrSsdMma, 4 * s + 1); break; }
@@ -200,14 +241,14 @@ ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) umma_ss(tS, dBt[kk], dXs[kk], id_z, 1u);
+        umma_commit(b_z_done);
         // Y += (G o decay o mask) . x
-        ok = mbar_wait(b_m_ready, ph, abort_flag);
+        ok = mbar_wait(b_x_full, ph, abort_flag) && mbar_wait(b_m_ready, ph, abort_flag);
         if (!ok) { ssd_report(status, kErrSsdMma, 4 * s + 3); break; }
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) umma_ts(tY, tR + kk * 8, dX[kk], id_m2, 1u);
         umma_commit(b_y_ready);
-        umma_commit(b_tiles_free);
       }
     }
     __syncwarp();
@@ -226,6 +267,9 @@ ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       tmem_wait_st();
     }
     bool ok = true;
+    float dt_next[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) dt_next[e] = dt[(static_cast<size_t>(b) * L + 4 * lane + e) * H + h];
     for (int s = 0; s < nsteps; ++s) {
       const uint32_t ph = s & 1;
       const size_t row0 = static_cast<size_t>(b) * L + static_cast<size_t>(s) * kQ;
@@ -233,7 +277,11 @@ ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       // ---- prefix sum of dt*A over the 128 rows, every warp for itself: lane l holds rows 4l..4l+3 ----
       float dt4[4], cum4[4];
 #pragma unroll
-      for (int e = 0; e < 4; ++e) dt4[e] = dt[(row0 + 4 * lane + e) * H + h];
+      for (int e = 0; e < 4; ++e) dt4[e] = dt_next[e];
+      if (s + 1 < nsteps) {  // the next step's dt, fetched a whole step ahead
+#pragma unroll
+        for (int e = 0; e < 4; ++e) dt_next[e] = dt[(row0 + kQ + 4 * lane + e) * H + h];
+      }
       cum4[0] = dt4[0] * a_log2;
 #pragma unroll
       for (int e = 1; e < 4; ++e) cum4[e] = cum4[e - 1] + dt4[e] * a_log2;
@@ -260,7 +308,7 @@ ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
         if (comp == e) { cum_i = cv; dt_i = dv; }
       }
 
-      ok = __all_sync(0xffffffffu, mbar_wait(b_tile_full, ph, abort_flag));
+      ok = __all_sync(0xffffffffu, mbar_wait(b_c_full, ph, abort_flag));
       if (!ok) { ssd_report(status, kErrSsdCompute, 8 * s); break; }
 
       // ---- E1a: C_i e^cum_i -> TMEM columns 0..63 (16 bit); S_in -> 16 bit in smem; S *= e^cum_last ----
@@ -306,24 +354,24 @@ ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
         mbar_arrive(b_e1a);
       }
 
-      // ---- E1b: w_i x_i -> smem (the buffer S_in occupied, free once the first product has retired) ----
-      ok = __all_sync(0xffffffffu, mbar_wait(b_inter_done, ph, abort_flag));
-      if (!ok) { ssd_report(status, kErrSsdCompute, 8 * s + 1); break; }
+      // ---- E1b: w_i x_i -> smem (the buffer S_in occupied, free once the first product has retired);
+      //      the scaled row is prepared in registers while that product runs ----
       {
+        ok = __all_sync(0xffffffffu, mbar_wait(b_x_full, ph, abort_flag));
+        if (!ok) { ssd_report(status, kErrSsdCompute, 8 * s + 4); break; }
         const float wi = ex2(total - cum_i) * dt_i;
+        uint4 xs[8];
 #pragma unroll
         for (int cc = 0; cc < 8; ++cc) {
           const uint4 w = *reinterpret_cast<const uint4 *>(pX + sw128(i, cc));
-          const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
-          uint4 o;
-          uint32_t *os = reinterpret_cast<uint32_t *>(&o);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float2 f = unpack2<DT>(ws[e]);
-            os[e] = pack2<DT>(f.x * wi, f.y * wi);
-          }
-          *reinterpret_cast<uint4 *>(pXs + sw128(i, cc)) = o;
+          const float2 f0 = unpack2<DT>(w.x), f1 = unpack2<DT>(w.y), f2 = unpack2<DT>(w.z), f3 = unpack2<DT>(w.w);
+          xs[cc] = make_uint4(pack2<DT>(f0.x * wi, f0.y * wi), pack2<DT>(f1.x * wi, f1.y * wi),
+                              pack2<DT>(f2.x * wi, f2.y * wi), pack2<DT>(f3.x * wi, f3.y * wi));
         }
+        ok = __all_sync(0xffffffffu, mbar_wait(b_inter_done, ph, abort_flag));
+        if (!ok) { ssd_report(status, kErrSsdCompute, 8 * s + 1); break; }
+#pragma unroll
+        for (int cc = 0; cc < 8; ++cc) *reinterpret_cast<uint4 *>(pXs + sw128(i, cc)) = xs[cc];
         fence_proxy_async_smem();
         mbar_arrive(b_e1b);
       }
@@ -363,7 +411,8 @@ ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       tc_fence_before();
       mbar_arrive(b_m_ready);
 
-      // ---- E3: Y -> storage dtype -> global (one 128-byte row per thread) ----
+      // ---- E3: Y -> storage dtype -> the buffer x occupied (x is dead once Y is complete);
+      //      the producer warp stores the tile with one TMA copy ----
       ok = __all_sync(0xffffffffu, mbar_wait(b_y_ready, ph, abort_flag));
       if (!ok) { ssd_report(status, kErrSsdCompute, 8 * s + 3); break; }
       tc_fence_after();
@@ -372,7 +421,6 @@ ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
         tmem_ld32p(tY + lane_addr, yv);
         tmem_ld32p(tY + lane_addr + 32, yv + 32);
         tmem_wait_ld();
-        uint16_t *dst = y + ((row0 + i) * H + h) * kP;
 #pragma unroll
         for (int cc = 0; cc < 8; ++cc) {
           uint4 w;
@@ -380,8 +428,10 @@ ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
           w.y = pack2<DT>(__uint_as_float(yv[8 * cc + 2]), __uint_as_float(yv[8 * cc + 3]));
           w.z = pack2<DT>(__uint_as_float(yv[8 * cc + 4]), __uint_as_float(yv[8 * cc + 5]));
           w.w = pack2<DT>(__uint_as_float(yv[8 * cc + 6]), __uint_as_float(yv[8 * cc + 7]));
-          *reinterpret_cast<uint4 *>(dst + cc * 8) = w;
+          *reinterpret_cast<uint4 *>(pX + sw128(i, cc)) = w;
         }
+        fence_proxy_async_smem();
+        mbar_arrive(b_y_staged);
       }
       tc_fence_before();  // orders these TMEM reads before the next step's products, via the e1a arrival
     }
@@ -399,15 +449,16 @@ ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
 template <int DT>
 int launch_ssd(const void *x, const float *dt, const float *A, const void *Bm, const void *Cm, void *y, int B, int L,
                int H, int G, int dtype, int *status, cudaStream_t st) {
-  CUtensorMap tx, tb, tc;
+  CUtensorMap tx, tb, tc, ty;
   int rc;
   if ((rc = tma_map_2d_sw128(&tx, x, (long long)B * L, (long long)H * kP, dtype, kQ, "ssd_chunk_scan")) != NB200_OK) return rc;
   if ((rc = tma_map_2d_sw128(&tb, Bm, (long long)B * L, (long long)G * kN, dtype, kQ, "ssd_chunk_scan")) != NB200_OK) return rc;
   if ((rc = tma_map_2d_sw128(&tc, Cm, (long long)B * L, (long long)G * kN, dtype, kQ, "ssd_chunk_scan")) != NB200_OK) return rc;
+  if ((rc = tma_map_2d_sw128(&ty, y, (long long)B * L, (long long)H * kP, dtype, kQ, "ssd_chunk_scan")) != NB200_OK) return rc;
   NB200_CHECK_CUDA(cudaFuncSetAttribute(ssd_fused_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSsdSmem));
   NB200_CHECK_CUDA(cudaFuncSetAttribute(ssd_fused_kernel<DT>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                         cudaSharedmemCarveoutMaxShared));
-  ssd_fused_kernel<DT><<<dim3(B * H), dim3(kSsdThreads), kSsdSmem, st>>>(tx, tb, tc, dt, A, static_cast<uint16_t *>(y),
+  ssd_fused_kernel<DT><<<dim3(B * H), dim3(kSsdThreads), kSsdSmem, st>>>(tx, tb, tc, ty, dt, A, static_cast<uint16_t *>(y),
                                                                          L, H, G, status);
   NB200_CHECK_CUDA(cudaGetLastError());
   return NB200_OK;
