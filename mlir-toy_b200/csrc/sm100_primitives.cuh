@@ -73,7 +73,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   const uint64_t t0 = globaltimer_ns();
 #pragma unroll 1
   while (true) {
-    if (mbar_try_wait_suspend(bar, parity, 200000u)) return true;  // wakes as soon as the phase completes
+    if (mbar_try_wait_suspend(bar, parity, 1000u)) return true;  // wakes as soon as the phase completes
     if (*abort_flag) return false;
     if (globaltimer_ns() - t0 > kWaitLimitNs) {
       *abort_flag = 1;
