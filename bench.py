@@ -384,7 +384,7 @@ def bench_extra(args, d: Dist, dev, flush, pk, pk_kind) -> dict:
 
     # -- Mamba-1 selective scan, (batch x channel) rows sharded as whole sequences when possible, else channels
     def run_scan():
-        c = SCAN
+        c = dict(SCAN, B=args.scan_batch) if args.scan_batch else SCAN
         if c["B"] % d.world == 0:
             Bl, Dl = c["B"] // d.world, c["Dm"]
         else:
@@ -440,6 +440,8 @@ def main() -> None:
     ap.add_argument("--skip-attention", action="store_true",
                     help="secondary workloads only (profiler captures of decode and the scans)")
     ap.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
+    ap.add_argument("--scan-batch", type=int, default=0,
+                    help="batch of the selective-scan workload (default: the full 8); reduced for profiler captures")
     ap.add_argument("--attn-units", type=int, default=0,
                     help="number of (batch, head) units of the attention workload (default: the full 256); "
                          "a reduced count is for profiler captures only and is recorded in config")
