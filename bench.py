@@ -48,9 +48,10 @@ SSD = dict(B=4, L=8192, H=64, P=64, N=128, G=1, chunk=256)  # configs[4]
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
-# DRAM bytes per launch of the attention kernel at the full configuration, from the ncu capture
-# summarised in profiles/ (None until a capture has been taken).
-ATTN_DRAM_TRAFFIC_BYTES = None
+# DRAM bytes per launch of the attention kernel at the full configuration: the ncu capture summarised in
+# profiles/attn_fwd_tcgen05_causal_bf16.md measured 250.8 MB read + written for 64 of the 256 (batch, head)
+# units; traffic grows in proportion to the unit count (K/V of a head stay in L2 while its tiles run).
+ATTN_DRAM_TRAFFIC_BYTES_PER_UNIT = 250_811_136 / 64
 
 
 def attn_flops(units: int, S: int, D: int) -> float:
@@ -246,7 +247,7 @@ def bench_attention(args, d: Dist, dev, flush, pk, pk_kind) -> dict:
     result = {
         "ms": ms, "value": value, "clocks": clocks.summary(),
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                     "traffic": ATTN_DRAM_TRAFFIC_BYTES, "peak_source": f"of {pk_kind} (burst cuBLAS bf16)",
+                     "traffic": ATTN_DRAM_TRAFFIC_BYTES_PER_UNIT * units, "peak_source": f"of {pk_kind} (burst cuBLAS bf16)",
                      "kernel": "attn_fwd_tcgen05_kernel<bf16>"},
     }
 
@@ -325,7 +326,7 @@ def bench_extra(args, d: Dist, dev, flush, pk, pk_kind) -> dict:
 
     # -- split-K decode, batch sharded over ranks
     def run_decode():
-        c = DECODE
+        c = dict(DECODE, B=args.decode_batch) if args.decode_batch else DECODE
         lo, hi = shard_range(c["B"], d.rank, d.world)
         Bl = hi - lo
         fn = load_callable(programs.decode_splitk_decl("decode", Bl, c["Hq"], c["Hkv"], c["L"], c["D"], c["S"]), "decode")
@@ -405,7 +406,7 @@ def bench_extra(args, d: Dist, dev, flush, pk, pk_kind) -> dict:
 
     # -- Mamba-2 SSD, heads sharded over ranks
     def run_ssd():
-        c = SSD
+        c = dict(SSD, B=args.ssd_batch) if args.ssd_batch else SSD
         lo, hi = shard_range(c["H"], d.rank, d.world)
         Hl = hi - lo
         ws_bytes = runtime.ssd_workspace_bytes(c["B"], c["L"], Hl, c["P"], c["N"], c["G"], c["chunk"])
@@ -440,6 +441,10 @@ def main() -> None:
     ap.add_argument("--skip-attention", action="store_true",
                     help="secondary workloads only (profiler captures of decode and the scans)")
     ap.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
+    ap.add_argument("--decode-batch", type=int, default=0,
+                    help="batch of the split-K decode workload (default: the full 64); reduced for profiler captures")
+    ap.add_argument("--ssd-batch", type=int, default=0,
+                    help="batch of the SSD workload (default: the full 4); reduced for profiler captures")
     ap.add_argument("--scan-batch", type=int, default=0,
                     help="batch of the selective-scan workload (default: the full 8); reduced for profiler captures")
     ap.add_argument("--attn-units", type=int, default=0,
