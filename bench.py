@@ -42,7 +42,8 @@ import torch.distributed as dist  # noqa: E402
 # ---- the benchmark configurations (BASELINE.json `configs`) ----------------------------------------
 ATTN = dict(B=8, H=32, S=4096, D=128)                       # configs[1]: causal bf16 prefill
 DECODE = dict(B=64, Hq=32, Hkv=8, L=32768, D=128, S=16)     # configs[2]
-DECODE1 = dict(B=1, Hq=32, Hkv=8, L=262144, D=128, S=16)    # configs[2], single-sequence variant
+DECODE1 = dict(B=1, Hq=32, Hkv=8, L=262144, D=128, S=64)    # configs[2], single-sequence variant: 64 splits
+                                                             # per GPU so that one sequence still fills the SMs
 SCAN = dict(B=8, Dm=4096, L=4096, N=16)                     # configs[3]
 SSD = dict(B=4, L=8192, H=64, P=64, N=128, G=1, chunk=256)  # configs[4]
 
