@@ -92,7 +92,7 @@ class ClockSampler:
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "20",
                  "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -105,6 +105,8 @@ class ClockSampler:
             self.lines.append(line.strip())
 
     def __exit__(self, *exc):
+        if self.proc is not None and not self.lines:
+            time.sleep(0.3)  # a very short timed region: wait for the first sample (the kernels are still the last thing that ran)
         if self.proc is not None:
             self.proc.terminate()
             try:
@@ -239,6 +241,13 @@ def bench_attention(args, d: Dist, dev, flush, pk, pk_kind) -> dict:
 
     with ClockSampler(dev.index) as clocks:
         ms = timed_steps(lambda: fn(q, k, v, out), args.steps, args.warmup, flush, d)
+        if len(clocks.lines) < 3:
+            # the timed region was shorter than the sampling period: keep the same kernel running (untimed)
+            # until a few samples under load exist
+            t_end = time.perf_counter() + 0.5
+            while time.perf_counter() < t_end and len(clocks.lines) < 5:
+                fn(q, k, v, out)
+                torch.cuda.synchronize()
     runtime.check_status(dev)
     flops_total = attn_flops(total_units, S, D)
     value = flops_total / (ms * 1e-3) / 1e12
