@@ -7,22 +7,25 @@
 // HBM traffic is tiny next to the arithmetic (one exp per state update), so the kernel is organised
 // around the special-function and fp32 pipes while keeping every global access a full coalesced
 // row segment:
-//   * one CTA = one sequence b and 32 channels d; 128 threads = 32 channels x 4 groups of 4 states;
-//     a thread keeps its 4 states and 4 decay rates in registers for the whole sequence;
+//   * one CTA = one sequence b and 32 channels d; 64 threads = 32 channels x 2 groups of 8 states;
+//     a thread keeps its 8 states and 8 decay rates in registers for the whole sequence (8 rather
+//     than 4 states per thread spreads the per-step scalar work over more updates: 5 % faster);
 //   * u, delta, z, Bm, Cm are staged through shared memory in chunks of 32 time steps with
 //     cp.async (16-byte, double-buffered), rows padded by 16 bytes so that the per-thread 128-bit
 //     reads are bank-conflict free; Bm/Cm are converted once per chunk to fp32 [t][n];
 //   * the state update runs on packed f32x2 FMAs; exp(delta*A) is one ex2 per update with A
 //     pre-multiplied by log2(e);
-//   * the sum over n is a transposing 4-lane butterfly (6 shuffles per 8 time steps) that leaves
-//     each lane two adjacent time steps, for which it applies the skip term and the SiLU gate and
-//     writes a packed pair into the output tile, stored to global memory as full rows.
+//   * the sum over n is finished by the two lanes of a channel swapping halves (4 shuffles per 8
+//     time steps), which leaves each lane four adjacent time steps, for which it applies the skip
+//     term and the SiLU gate and writes two packed pairs into the output tile, stored to global
+//     memory as full rows.
 #include "nb200_common.cuh"
 
 namespace nb200 {
 namespace {
 
-constexpr int kScanThreads = 128;
+constexpr int kScanThreads = 64;
+constexpr int kNPT = 8;                       // states per thread (two threads per channel)
 constexpr int kDB = 32;                       // channels per CTA
 constexpr int kLC = 32;                       // time steps per staged chunk
 constexpr int kRowBytes = kLC * 2 + 16;       // padded row of a 16-bit tile
@@ -54,7 +57,7 @@ template <int N> __device__ __forceinline__ void cp_async_wait() {
 }
 
 template <int DT>
-__global__ void __launch_bounds__(kScanThreads, 7)
+__global__ void __launch_bounds__(kScanThreads, 10)
 selective_scan_kernel(const uint16_t *__restrict__ u, const uint16_t *__restrict__ delta,
                       const float *__restrict__ A, const uint16_t *__restrict__ Bm,
                       const uint16_t *__restrict__ Cm, const float *__restrict__ Dskip,
@@ -63,14 +66,16 @@ selective_scan_kernel(const uint16_t *__restrict__ u, const uint16_t *__restrict
   const int tid = threadIdx.x;
   const int b = blockIdx.y;
   const int d0 = blockIdx.x * kDB;
-  const int dl = tid >> 2, ng = tid & 3;
+  const int dl = tid >> 1, ng = tid & 1;
   const int d = d0 + dl;
 
   // decay rates of this thread's 4 states, in the exp2 domain, as two packed pairs
-  const float4 a4 = *reinterpret_cast<const float4 *>(A + (size_t)d * kStates + ng * 4);
-  const uint64_t A2[2] = {f2_pack(a4.x * kLog2e, a4.y * kLog2e), f2_pack(a4.z * kLog2e, a4.w * kLog2e)};
+  const float4 a4 = *reinterpret_cast<const float4 *>(A + (size_t)d * kStates + ng * kNPT);
+  const float4 a5 = *reinterpret_cast<const float4 *>(A + (size_t)d * kStates + ng * kNPT + 4);
+  const uint64_t A2[4] = {f2_pack(a4.x * kLog2e, a4.y * kLog2e), f2_pack(a4.z * kLog2e, a4.w * kLog2e),
+                          f2_pack(a5.x * kLog2e, a5.y * kLog2e), f2_pack(a5.z * kLog2e, a5.w * kLog2e)};
   const float dskip = Dskip[d];
-  uint64_t h2[2] = {0ull, 0ull};
+  uint64_t h2[4] = {0ull, 0ull, 0ull, 0ull};
 
   const size_t row_base = ((size_t)b * Dm + d0) * L;        // element offset of row d0 of this sequence
   const size_t bc_base = (size_t)b * kStates * L;
@@ -79,18 +84,19 @@ selective_scan_kernel(const uint16_t *__restrict__ u, const uint16_t *__restrict
   auto issue_loads = [&](int chunk, int buf) {
     ScanStage &s = sm.stage[buf];
     const int t0 = chunk * kLC;
-    {  // u / delta / z : 32 rows x 4 segments of 16 bytes -> one per thread per tensor
-      const int row = tid >> 2, seg = tid & 3;
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {  // u / delta / z : 32 rows x 4 segments of 16 bytes -> two per thread per tensor
+      const int idx = tid + k * kScanThreads, row = idx >> 2, seg = idx & 3;
       const size_t g = row_base + (size_t)row * L + t0 + seg * 8;
       cp_async16(s.u + row * kRowBytes + seg * 16, u + g);
       cp_async16(s.dl + row * kRowBytes + seg * 16, delta + g);
       cp_async16(s.z + row * kRowBytes + seg * 16, z + g);
     }
-    {  // Bm (threads 0..63) and Cm (threads 64..127): 16 rows x 4 segments each
-      const int i = tid & 63, row = i >> 2, seg = i & 3;
+    {  // Bm and Cm: 16 rows x 4 segments each -> one of each per thread
+      const int row = tid >> 2, seg = tid & 3;
       const size_t g = bc_base + (size_t)row * L + t0 + seg * 8;
-      if (tid < 64) cp_async16(s.braw + row * (kLC * 2) + seg * 16, Bm + g);
-      else cp_async16(s.craw + row * (kLC * 2) + seg * 16, Cm + g);
+      cp_async16(s.braw + row * (kLC * 2) + seg * 16, Bm + g);
+      cp_async16(s.craw + row * (kLC * 2) + seg * 16, Cm + g);
     }
     cp_async_commit();
   };
@@ -107,20 +113,19 @@ selective_scan_kernel(const uint16_t *__restrict__ u, const uint16_t *__restrict
     __syncthreads();
     ScanStage &s = sm.stage[buf];
 
-    {  // Bm/Cm of this chunk -> fp32 [t][n]; thread = (n, group of 4 time steps)
-      const int n = tid >> 3, tq = tid & 7;
-      const uint2 bw = *reinterpret_cast<const uint2 *>(s.braw + n * (kLC * 2) + tq * 8);
-      const uint2 cw = *reinterpret_cast<const uint2 *>(s.craw + n * (kLC * 2) + tq * 8);
-      const float2 b01 = unpack2<DT>(bw.x), b23 = unpack2<DT>(bw.y);
-      const float2 c01 = unpack2<DT>(cw.x), c23 = unpack2<DT>(cw.y);
-      sm.bf[tq * 4 + 0][n] = b01.x;
-      sm.bf[tq * 4 + 1][n] = b01.y;
-      sm.bf[tq * 4 + 2][n] = b23.x;
-      sm.bf[tq * 4 + 3][n] = b23.y;
-      sm.cf[tq * 4 + 0][n] = c01.x;
-      sm.cf[tq * 4 + 1][n] = c01.y;
-      sm.cf[tq * 4 + 2][n] = c23.x;
-      sm.cf[tq * 4 + 3][n] = c23.y;
+    {  // Bm/Cm of this chunk -> fp32 [t][n]; thread = (n, group of 8 time steps)
+      const int n = tid >> 2, tq = tid & 3;
+      const uint4 bw = *reinterpret_cast<const uint4 *>(s.braw + n * (kLC * 2) + tq * 16);
+      const uint4 cw = *reinterpret_cast<const uint4 *>(s.craw + n * (kLC * 2) + tq * 16);
+      const uint32_t bs[4] = {bw.x, bw.y, bw.z, bw.w}, cs[4] = {cw.x, cw.y, cw.z, cw.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 bb = unpack2<DT>(bs[e]), cc = unpack2<DT>(cs[e]);
+        sm.bf[tq * 8 + 2 * e][n] = bb.x;
+        sm.bf[tq * 8 + 2 * e + 1][n] = bb.y;
+        sm.cf[tq * 8 + 2 * e][n] = cc.x;
+        sm.cf[tq * 8 + 2 * e + 1][n] = cc.y;
+      }
     }
     __syncthreads();
 
@@ -142,12 +147,14 @@ selective_scan_kernel(const uint16_t *__restrict__ u, const uint16_t *__restrict
           const uint64_t dt2 = f2_pack(dd[e], dd[e]);
           const float dtu = dd[e] * uu[e];
           const uint64_t dtu2 = f2_pack(dtu, dtu);
-          const ulonglong2 bv = *reinterpret_cast<const ulonglong2 *>(&sm.bf[t][ng * 4]);
-          const ulonglong2 cv = *reinterpret_cast<const ulonglong2 *>(&sm.cf[t][ng * 4]);
-          const uint64_t b2[2] = {bv.x, bv.y}, c2[2] = {cv.x, cv.y};
+          const ulonglong2 bv = *reinterpret_cast<const ulonglong2 *>(&sm.bf[t][ng * kNPT]);
+          const ulonglong2 bw = *reinterpret_cast<const ulonglong2 *>(&sm.bf[t][ng * kNPT + 4]);
+          const ulonglong2 cv = *reinterpret_cast<const ulonglong2 *>(&sm.cf[t][ng * kNPT]);
+          const ulonglong2 cw = *reinterpret_cast<const ulonglong2 *>(&sm.cf[t][ng * kNPT + 4]);
+          const uint64_t b2[4] = {bv.x, bv.y, bw.x, bw.y}, c2[4] = {cv.x, cv.y, cw.x, cw.y};
           uint64_t y2 = 0ull;
 #pragma unroll
-          for (int i = 0; i < 2; ++i) {
+          for (int i = 0; i < 4; ++i) {
             const float2 x = f2_unpack(f2_mul(dt2, A2[i]));
             const uint64_t a2 = f2_pack(ex2(x.x), ex2(x.y));
             h2[i] = f2_fma(a2, h2[i], f2_mul(dtu2, b2[i]));
@@ -157,35 +164,33 @@ selective_scan_kernel(const uint16_t *__restrict__ u, const uint16_t *__restrict
           y8[tp * 2 + e] = yy.x + yy.y;
         }
       }
-      // Transposing butterfly over the 4 lanes of a channel: lane ng ends with t = 2*ng, 2*ng+1.
-      const bool hi2 = ng & 2, hi1 = ng & 1;
-      float k4[4];
+      // The two lanes of a channel exchange halves: lane ng ends with t = 4*ng .. 4*ng+3.
+      float r4[4];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const float keep = hi2 ? y8[4 + i] : y8[i];
-        const float send = hi2 ? y8[i] : y8[4 + i];
-        k4[i] = keep + __shfl_xor_sync(0xffffffffu, send, 2);
+        const float keep = ng ? y8[4 + i] : y8[i];
+        const float send = ng ? y8[i] : y8[4 + i];
+        r4[i] = keep + __shfl_xor_sync(0xffffffffu, send, 1);
       }
-      float r2[2];
+      // skip term and SiLU gate for this lane's four time steps
+      const int off = dl * kRowBytes + t8 * 16 + ng * 8;
+      const uint2 uw2 = *reinterpret_cast<const uint2 *>(s.u + off);
+      const uint2 zw2 = *reinterpret_cast<const uint2 *>(s.z + off);
+      const float2 ua = unpack2<DT>(uw2.x), ub = unpack2<DT>(uw2.y), za = unpack2<DT>(zw2.x), zb = unpack2<DT>(zw2.y);
+      const float uu4[4] = {ua.x, ua.y, ub.x, ub.y}, zz4[4] = {za.x, za.y, zb.x, zb.y};
+      float o4[4];
 #pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const float keep = hi1 ? k4[2 + i] : k4[i];
-        const float send = hi1 ? k4[i] : k4[2 + i];
-        r2[i] = keep + __shfl_xor_sync(0xffffffffu, send, 1);
+      for (int i = 0; i < 4; ++i) {
+        const float yv = fmaf(dskip, uu4[i], r4[i]);
+        o4[i] = yv * zz4[i] * __frcp_rn(1.f + ex2(-zz4[i] * kLog2e));
       }
-      // skip term and SiLU gate for this lane's two time steps
-      const int off = dl * kRowBytes + t8 * 16 + ng * 4;
-      const float2 u2 = unpack2<DT>(*reinterpret_cast<const uint32_t *>(s.u + off));
-      const float2 z2 = unpack2<DT>(*reinterpret_cast<const uint32_t *>(s.z + off));
-      const float y0 = fmaf(dskip, u2.x, r2[0]), y1 = fmaf(dskip, u2.y, r2[1]);
-      const float g0 = z2.x * __frcp_rn(1.f + ex2(-z2.x * kLog2e));
-      const float g1 = z2.y * __frcp_rn(1.f + ex2(-z2.y * kLog2e));
-      *reinterpret_cast<uint32_t *>(sm.out + off) = pack2<DT>(y0 * g0, y1 * g1);
+      *reinterpret_cast<uint2 *>(sm.out + off) = make_uint2(pack2<DT>(o4[0], o4[1]), pack2<DT>(o4[2], o4[3]));
     }
     __syncthreads();
 
-    {  // output tile -> global, one 16-byte segment per thread (rows are 64 contiguous bytes)
-      const int row = tid >> 2, seg = tid & 3;
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {  // output tile -> global, two 16-byte segments per thread (rows are 64 contiguous bytes)
+      const int idx = tid + k * kScanThreads, row = idx >> 2, seg = idx & 3;
       const uint4 w = *reinterpret_cast<const uint4 *>(sm.out + row * kRowBytes + seg * 16);
       *reinterpret_cast<uint4 *>(out + row_base + (size_t)row * L + chunk * kLC + seg * 8) = w;
     }
