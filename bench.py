@@ -429,7 +429,7 @@ def bench_extra(args, d: Dist, dev, flush, pk, pk_kind) -> dict:
         y = torch.empty_like(x)
         ms = timed_steps(lambda: fn(x, dt, A, Bm, Cm, ws, y), steps, warm, flush, d)
         total = 2 * c["B"] * c["L"] * c["H"] * c["P"] * 2 + c["B"] * c["L"] * c["H"] * 4 + 2 * c["B"] * c["L"] * c["G"] * c["N"] * 2 + c["H"] * 4
-        record("ssd_chunk_scan", ms, total, {"config": "B=4 L=8192 H=64 P=64 N=128 chunk=256 (configs[4])", "launches_per_step": 3})
+        record("ssd_chunk_scan", ms, total, {"config": "B=4 L=8192 H=64 P=64 N=128 chunk=256 (configs[4])", "launches_per_step": 1})
 
     for name, fn_ in (("decode", run_decode), ("decode1", run_decode1), ("scan", run_scan), ("ssd", run_ssd)):
         if name in want:
