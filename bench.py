@@ -316,7 +316,7 @@ def bench_attention(args, d: Dist, dev, flush, pk, pk_kind) -> dict:
 def bench_extra(args, d: Dist, dev, flush, pk, pk_kind) -> dict:
     """Decode and both scans at their configurations (HBM-bound by the metric): GB/s of algorithmic bytes."""
     from neptune_mlir import programs, runtime
-    from neptune_mlir.sharding import gather_partials, gathered_strides, shard_range
+    from neptune_mlir.sharding import shard_range
 
     steps, warm = max(3, min(args.steps, 10)), 3
     hbm = pk["hbm_gbs"]
@@ -373,11 +373,15 @@ def bench_extra(args, d: Dist, dev, flush, pk, pk_kind) -> dict:
             runtime.decode_combine(part, local, rows=rows, D=c["D"], n_splits=c["S"], row_stride=c["S"] * (c["D"] + 2),
                                    split_stride=c["D"] + 2, out_dtype="f32")
 
+        comm = gathered = None
+        if d.world > 1:
+            from neptune_mlir.nccl_comm import Communicator
+            comm = Communicator.from_process_group()
+            gathered = torch.empty((d.world, rows, c["D"] + 2), device=dev)
+
         def merge_part():
             if d.world > 1:
-                g = gather_partials(local)
-                rs, ss = gathered_strides(rows, c["D"] + 2)
-                runtime.decode_combine(g, o, rows=rows, D=c["D"], n_splits=d.world, row_stride=rs, split_stride=ss, out_dtype="bf16")
+                runtime.decode_merge_nccl(local, gathered, o, rows=rows, D=c["D"], world=d.world, out_dtype="bf16", comm=comm)
             else:
                 runtime.decode_combine(local, o, rows=rows, D=c["D"], n_splits=1, row_stride=c["D"] + 2,
                                        split_stride=c["D"] + 2, out_dtype="bf16")
@@ -389,8 +393,11 @@ def bench_extra(args, d: Dist, dev, flush, pk, pk_kind) -> dict:
         record("decode_single_sequence", ms_both, total,
                {"config": "B=1 L=262144 KV sharded along L over ranks (configs[2] variant)", "stream_ms": ms_stream,
                 "merge_ms": ms_merge, "merge_bytes_per_rank": rows * (c["D"] + 2) * 4,
-                "collective": "all_gather (NCCL)" if d.world > 1 else "none"})
-        del q, k, v, part, local, o
+                "collective": "ncclAllGather inside nb200_decode_merge_nccl" if d.world > 1 else "none"})
+        if comm is not None:
+            torch.cuda.synchronize(dev)
+            comm.destroy()
+        del q, k, v, part, local, o, gathered
         torch.cuda.empty_cache()
 
     # -- Mamba-1 selective scan, (batch x channel) rows sharded as whole sequences when possible, else channels

@@ -30,6 +30,7 @@ extern "C" {
 #define NB200_ERR_UNSUPPORTED (-2)    /* shape / dtype outside what the kernels implement        */
 #define NB200_ERR_LAUNCH (-3)         /* the CUDA runtime or driver rejected a call              */
 #define NB200_ERR_DEVICE_TIMEOUT (-4) /* a bounded device-side wait expired (see status word)    */
+#define NB200_ERR_NCCL (-5)           /* NCCL could not be loaded, or a collective call failed   */
 
 /* dtype codes: element type of the storage tensors */
 #define NB200_F16 0
@@ -96,6 +97,24 @@ int nb200_decode_splitk(const void *q, const void *k, const void *v, float *part
  */
 int nb200_decode_combine(const float *partials, void *out, int rows, int D, int n_splits,
                          long long row_stride, long long split_stride, int out_dtype, void *stream);
+
+/*
+ * Merge of a single-sequence decode whose KV cache is split along its length over the ranks of an
+ * NCCL communicator (no counterpart in the reference).  Each rank first runs nb200_decode_splitk on
+ * its slice and nb200_decode_combine with out_dtype NB200_F32, which leaves one partial per query
+ * head; this call all-gathers them and combines across ranks, so every rank ends with the output.
+ *
+ *   local_partial : fp32 [rows, D + 2], this rank's partials (rows = B * Hq)
+ *   gathered      : fp32 [world, rows, D + 2] scratch (nb200_decode_merge_workspace_bytes)
+ *   out           : [rows, D] in out_dtype (or [rows, D + 2] fp32 for NB200_F32)
+ *   nccl_comm     : the caller's ncclComm_t, whose size must equal `world`
+ * NCCL is resolved at run time from the library the process has loaded (else $NEPTUNE_B200_NCCL, else
+ * libnccl.so.2); the collective and the combine kernel are enqueued on `stream`.  Like every NCCL
+ * collective, all ranks of the communicator must make the call.
+ */
+size_t nb200_decode_merge_workspace_bytes(int rows, int D, int world);
+int nb200_decode_merge_nccl(const float *local_partial, float *gathered, void *out, int rows, int D,
+                            int world, int out_dtype, void *nccl_comm, void *stream);
 
 /*
  * Split-K decode plus combine for callers that may not allocate (no counterpart in the reference).

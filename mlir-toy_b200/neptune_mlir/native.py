@@ -14,7 +14,7 @@ from pathlib import Path
 from .plugin import find_library_path
 
 NB200_OK = 0
-ERROR_NAMES = {-1: "bad argument", -2: "unsupported", -3: "launch failure", -4: "device wait timeout"}
+ERROR_NAMES = {-1: "bad argument", -2: "unsupported", -3: "launch failure", -4: "device wait timeout", -5: "NCCL failure"}
 DTYPE_CODES = {"f16": 0, "bf16": 1, "f32": 2}
 STATUS_WORDS = 4
 
@@ -30,6 +30,9 @@ SYMBOLS: dict[str, tuple] = {
                                     c_int, c_int, c_float, c_void_p]),
     "nb200_decode_combine": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_int,
                                      c_void_p]),
+    "nb200_decode_merge_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "nb200_decode_merge_nccl": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
+                                        c_void_p]),
     "nb200_decode_fwd_static": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                         c_int, c_int, c_float, c_void_p]),
     "nb200_selective_scan_fwd": (c_int, [c_void_p] * 8 + [c_int] * 5 + [c_void_p]),

@@ -124,6 +124,19 @@ def decode_combine(partials, out, *, rows, D, n_splits, row_stride, split_stride
     native.check(rc, "nb200_decode_combine")
 
 
+def decode_merge_nccl(local_partial, gathered, out, *, rows, D, world, out_dtype, comm) -> None:
+    """All-gather per-rank partials over ``comm`` (a ``nccl_comm.Communicator``) and combine across ranks."""
+    _check("local_partial", local_partial, (rows, D + 2), torch.float32)
+    _check("gathered", gathered, (world, rows, D + 2), torch.float32)
+    _check("out", out, (rows, D + 2 if out_dtype == "f32" else D), out_dtype)
+    dev = _same_device(local_partial, gathered, out)
+    with torch.cuda.device(dev):
+        rc = native.lib().nb200_decode_merge_nccl(local_partial.data_ptr(), gathered.data_ptr(), out.data_ptr(),
+                                                  rows, D, world, native.DTYPE_CODES[out_dtype], comm.handle,
+                                                  _stream(dev))
+    native.check(rc, "nb200_decode_merge_nccl")
+
+
 def selective_scan(u, delta, A, Bm, Cm, Dskip, z, out, *, B, Dm, L, N, dtype) -> None:
     """Mamba-1 selective scan forward (layouts in include/nb200.h)."""
     _check("u", u, (B, Dm, L), dtype)

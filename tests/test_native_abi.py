@@ -68,6 +68,29 @@ def test_version_and_argument_errors_without_a_gpu(native_lib):
         native.check(rc, "attn")
 
 
+def test_nccl_merge_rejects_bad_calls_without_a_gpu(native_lib):
+    lib = native.load(str(native_lib))
+    buf = ctypes.create_string_buffer(64)
+    p = ctypes.addressof(buf)
+    p += (-p) % 16
+    assert lib.nb200_decode_merge_workspace_bytes(32, 128, 8) == 8 * 32 * 130 * 4
+    assert lib.nb200_decode_merge_workspace_bytes(0, 128, 8) == 0
+    rc = lib.nb200_decode_merge_nccl(p, p, p, 32, 128, 2, 1, None, None)
+    assert rc == -1 and b"null communicator" in lib.nb200_last_error()
+    rc = lib.nb200_decode_merge_nccl(p, p, p, 32, 64, 2, 1, p, None)
+    assert rc == -2 and b"only 128" in lib.nb200_last_error()
+    rc = lib.nb200_decode_merge_nccl(None, p, p, 32, 128, 2, 1, p, None)
+    assert rc == -1
+
+
+def test_nccl_communicator_argument_checks():
+    from neptune_mlir import nccl_comm
+    with pytest.raises(ValueError, match="128 bytes"):
+        nccl_comm.Communicator(0, 2, b"short")
+    with pytest.raises(ValueError, match="outside world"):
+        nccl_comm.Communicator(2, 2, bytes(128))
+
+
 def test_workspace_sizes(native_lib):
     lib = native.load(str(native_lib))
     assert lib.nb200_decode_workspace_bytes(64, 32, 128, 16) == 64 * 32 * 16 * 130 * 4
