@@ -40,6 +40,26 @@ def test_reference_shape_f16_matches_reference_golden_tiles(cuda, native_lib):
         torch.testing.assert_close(out[:, head:head + 1].float().cpu(), ref, rtol=0, atol=REF_F16_ATOL)
 
 
+def test_other_shapes_match_kernels_emitted_by_the_reference_translator(cuda, native_lib):
+    """fp32 1x4x256x64 (exact-fp32 kernel) and f16 2x4x512x128 (tcgen05 kernel), non-causal, against outputs of the
+    kernels the unmodified reference translator emitted for the same HTile programs (Triton interpreter, CPU)."""
+    from neptune_mlir import programs
+
+    g = np.load(Path(__file__).parent / "golden" / "reference_translations.npz")
+    for name, dtype_name, dtype, atol in (("f32_1x4x256x64", "f32", torch.float32, F32_ATOL),
+                                          ("f16_2x4x512x128", "f16", torch.float16, REF_F16_ATOL)):
+        B, H, S, D, tm, tn, cfg = (int(x) for x in g[f"{name}.spec"])
+        q, k, v = inputs.attention_inputs(B, H, S, D, dtype, config=cfg)
+        fn = f"attn_{name}"
+        mod = translate_text(programs.attention_htile(fn, B, H, S, D, dtype_name, causal=False, tile_m=tm, tile_n=tn),
+                             f"translated_{fn}")
+        out = torch.full((B, H, S, D), float("nan"), dtype=dtype, device=cuda)
+        getattr(mod, fn)(q.to(cuda), k.to(cuda), v.to(cuda), out)
+        finish()
+        want = torch.from_numpy(g[f"{name}.out"]).float()
+        torch.testing.assert_close(out.float().cpu(), want, rtol=0, atol=atol)
+
+
 def test_config1_fp32_causal(cuda, native_lib):
     """B=1, H=4, S=256, D=64 fp32 causal (exact-fp32 kernel)."""
     q, k, v = inputs.attention_inputs(1, 4, 256, 64, torch.float32, config=1)

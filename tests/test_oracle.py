@@ -38,6 +38,32 @@ def test_attention_oracle_matches_reference_golden_tiles():
         assert (prog - want).abs().max() <= 2 ** -13
 
 
+TRANSLATIONS = Path(__file__).parent / "golden" / "reference_translations.npz"
+TRANSLATION_CASES = {"f32_1x4x256x64": (torch.float32, 1e-4), "f16_2x4x512x128": (torch.float16, 1e-3)}
+
+
+def _sha_bytes(*tensors):
+    h = hashlib.sha256()
+    for t in tensors:
+        h.update(t.contiguous().view(torch.uint8).numpy().tobytes())
+    return h.hexdigest()
+
+
+def test_attention_oracle_matches_reference_translator_at_other_shapes():
+    """Outputs of kernels that the UNMODIFIED reference translator emitted for fp32 and for another f16 shape
+    (tests/golden/make_reference_translations.py), run over their whole grids by the Triton interpreter."""
+    g = np.load(TRANSLATIONS)
+    for name, (dtype, atol) in TRANSLATION_CASES.items():
+        B, H, S, D, tm, tn, cfg = (int(x) for x in g[f"{name}.spec"])
+        q, k, v = inputs.attention_inputs(B, H, S, D, dtype, config=cfg)
+        assert _sha_bytes(q, k, v) == str(g[f"{name}.inputs_sha256"])
+        want = torch.from_numpy(g[f"{name}.out"]).float()
+        ref = attention.attention_reference(q, k, v)
+        prog = attention.attention_program(q, k, v, kv_block=tn).float()
+        torch.testing.assert_close(ref, want, rtol=0, atol=atol)
+        torch.testing.assert_close(prog, want, rtol=0, atol=atol)
+
+
 def test_attention_forms_agree_causal_and_not():
     for dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 2e-2), (torch.float16, 2e-3)):
         q, k, v = inputs.attention_inputs(1, 2, 256, 64, dtype, config=1)
