@@ -42,7 +42,8 @@ import torch.distributed as dist  # noqa: E402
 # ---- the benchmark configurations (BASELINE.json `configs`) ----------------------------------------
 ATTN = dict(B=8, H=32, S=4096, D=128)                       # configs[1]: causal bf16 prefill
 DECODE = dict(B=64, Hq=32, Hkv=8, L=32768, D=128, S=16)     # configs[2]
-DECODE1 = dict(B=1, Hq=32, Hkv=8, L=262144, D=128, S=64)    # configs[2], single-sequence variant: 64 splits
+DECODE1 = dict(B=1, Hq=32, Hkv=8, L=262144, D=128)          # configs[2], single-sequence variant
+DECODE1_WAVES = 1                                            # splits = waves * (resident CTA slots / kv heads)
                                                              # per GPU so that one sequence still fills the SMs
 SCAN = dict(B=8, Dm=4096, L=4096, N=16)                     # configs[3]
 SSD = dict(B=4, L=8192, H=64, P=64, N=128, G=1, chunk=256)  # configs[4]
@@ -351,7 +352,10 @@ def bench_extra(args, d: Dist, dev, flush, pk, pk_kind) -> dict:
 
     # -- single sequence, KV sharded along L over ranks, partials merged over NCCL
     def run_decode1():
-        c = DECODE1
+        c = dict(DECODE1)
+        # one CTA per (split, kv head); two CTAs are resident per SM: fill those slots a whole number of times
+        slots = 2 * torch.cuda.get_device_properties(dev).multi_processor_count
+        c["S"] = args.decode1_splits or max(1, slots // c["Hkv"]) * DECODE1_WAVES
         lo, hi = shard_range(c["L"], d.rank, d.world)
         Ll = hi - lo
         rows = c["Hq"]
@@ -391,7 +395,7 @@ def bench_extra(args, d: Dist, dev, flush, pk, pk_kind) -> dict:
         ms_both = timed_steps(lambda: (stream_part(), merge_part()), steps, warm, flush, d)
         total = 2 * c["Hkv"] * c["L"] * c["D"] * 2 + 2 * c["Hq"] * c["D"] * 2
         record("decode_single_sequence", ms_both, total,
-               {"config": "B=1 L=262144 KV sharded along L over ranks (configs[2] variant)", "stream_ms": ms_stream,
+               {"config": f"B=1 L=262144 KV sharded along L over ranks, {c['S']} splits per rank (configs[2] variant)", "stream_ms": ms_stream,
                 "merge_ms": ms_merge, "merge_bytes_per_rank": rows * (c["D"] + 2) * 4,
                 "collective": "ncclAllGather inside nb200_decode_merge_nccl" if d.world > 1 else "none"})
         if comm is not None:
@@ -452,6 +456,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=("native", "reference"), default="native")
     ap.add_argument("--skip-extra", action="store_true", help="attention only (skip decode and the scans)")
+    ap.add_argument("--decode1-splits", type=int, default=0, help="splits of the single-sequence decode (0 = fill the SMs once)")
     ap.add_argument("--extra", default="decode,decode1,scan,ssd",
                     help="comma list of the secondary workloads to run (decode, decode1, scan, ssd)")
     ap.add_argument("--skip-cpu", action="store_true", help="skip the CPU baseline leg")

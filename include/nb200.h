@@ -78,7 +78,8 @@ int nb200_status_read(const int *status, int *host_out, void *stream);
  *   partials : fp32 [B, Hq, n_splits, D + 2]; per (b, hq, split) the un-normalised output o[D]
  *              followed by m (running maximum, exp2 domain) and l (sum of 2^(x - m))
  *   scale_log2 : log2(e) * softmax scale
- * Lkv must be a multiple of n_splits, and Lkv / n_splits a multiple of 16.
+ * Split s covers KV rows [floor(s*Lkv/n_splits), floor((s+1)*Lkv/n_splits)); n_splits <= Lkv, otherwise free
+ * (choose it so that n_splits * Hkv * B fills the GPU's resident CTA slots, two per SM, a whole number of times).
  */
 size_t nb200_decode_workspace_bytes(int B, int Hq, int D, int n_splits);
 

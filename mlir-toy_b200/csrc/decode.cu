@@ -40,7 +40,10 @@ decode_splitk_kernel(const uint16_t *__restrict__ q, const uint16_t *__restrict_
                      int n_splits, float scale_log2) {
   const int split = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
   const int Hq = Hkv * G;
-  const int T = Lkv / n_splits;
+  // split s covers rows [floor(s*L/n), floor((s+1)*L/n)): equal parts when n divides L, else parts that
+  // differ by one row, so that the caller can choose n for the machine (one CTA per resident slot)
+  const int t0 = static_cast<int>((long long)split * Lkv / n_splits);
+  const int T = static_cast<int>((long long)(split + 1) * Lkv / n_splits) - t0;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int half = lane >> 4, c = lane & 15;
 
@@ -57,7 +60,7 @@ decode_splitk_kernel(const uint16_t *__restrict__ q, const uint16_t *__restrict_
     }
   }
 
-  const size_t kv_base = (((size_t)b * Hkv + hkv) * Lkv + (size_t)split * T) * kHeadDim + c * 8;
+  const size_t kv_base = (((size_t)b * Hkv + hkv) * Lkv + (size_t)t0) * kHeadDim + c * 8;
   const uint16_t *kp = k + kv_base;
   const uint16_t *vp = v + kv_base;
 
@@ -344,8 +347,8 @@ extern "C" int nb200_decode_splitk(const void *q, const void *k, const void *v, 
                 "decode_splitk: q/k/v must be 16-byte aligned");
   NB200_REQUIRE(D == kHeadDim, NB200_ERR_UNSUPPORTED, "decode_splitk: D = %d, only 128 is implemented", D);
   NB200_REQUIRE(Hq % Hkv == 0, NB200_ERR_UNSUPPORTED, "decode_splitk: Hq %% Hkv != 0");
-  NB200_REQUIRE(Lkv % n_splits == 0 && (Lkv / n_splits) % 16 == 0, NB200_ERR_UNSUPPORTED,
-                "decode_splitk: Lkv/n_splits must be a whole multiple of 16");
+  NB200_REQUIRE(n_splits <= Lkv, NB200_ERR_UNSUPPORTED, "decode_splitk: more splits (%d) than KV rows (%d)",
+                n_splits, Lkv);
   NB200_REQUIRE(Hkv <= 65535 && B <= 65535, NB200_ERR_UNSUPPORTED, "decode_splitk: grid too large");
   auto st = static_cast<cudaStream_t>(stream);
   if (dtype == NB200_BF16) return launch_splitk<NB200_BF16>(q, k, v, partials, B, Hq, Hkv, Lkv, n_splits, scale_log2, st);

@@ -45,13 +45,14 @@ def decode_reference(q, k, v, scale: float | None = None, kv_chunk: int = 4096):
 def decode_partials(q, k, v, n_splits: int, scale: float | None = None):
     """Per-split (m, l, o): x_t = q.k_t*scale, m_s = max x_t, l_s = sum e^(x_t-m_s), o_s = sum e^(x_t-m_s) v_t.
 
+    Split s covers rows [floor(s*L/n), floor((s+1)*L/n)).
     Returns m, l [B,Hq,n_splits] and o [B,Hq,n_splits,D], all fp32, natural-exponent domain.
     """
     B, Hq, D = q.shape
     Hkv, L = k.shape[1], k.shape[2]
     group = Hq // Hkv
-    assert L % n_splits == 0
-    T = L // n_splits
+    assert 0 < n_splits <= L
+    edges = [s * L // n_splits for s in range(n_splits + 1)]
     scale = 1.0 / math.sqrt(D) if scale is None else scale
     m = torch.empty((B, Hq, n_splits))
     l = torch.empty((B, Hq, n_splits))
@@ -59,8 +60,8 @@ def decode_partials(q, k, v, n_splits: int, scale: float | None = None):
     for b in range(B):
         qg = q[b].float().view(Hkv, group, D)
         for s in range(n_splits):
-            kc = k[b, :, s * T:(s + 1) * T].float()
-            vc = v[b, :, s * T:(s + 1) * T].float()
+            kc = k[b, :, edges[s]:edges[s + 1]].float()
+            vc = v[b, :, edges[s]:edges[s + 1]].float()
             x = torch.matmul(qg, kc.transpose(-1, -2)) * scale
             ms = x.amax(dim=-1)
             p = torch.exp(x - ms[..., None])

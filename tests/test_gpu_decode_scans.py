@@ -50,6 +50,25 @@ def test_decode_ragged_split_and_f16(cuda, native_lib):
     assert_storage_close(out, decode.decode_reference(q, k, v), 2e-3)
 
 
+def test_decode_splits_that_do_not_divide_the_length(cuda, native_lib):
+    """n_splits = 37 over 1000 rows: parts of 27 and 28 rows, per-split partials checked against the oracle."""
+    from neptune_mlir import runtime
+
+    B, Hq, Hkv, L, D, S = 2, 8, 2, 1000, 128, 37
+    q, k, v = inputs.decode_inputs(B=B, Hq=Hq, Hkv=Hkv, L=L, D=D, dtype=torch.bfloat16)
+    partials = torch.full((B, Hq, S, D + 2), float("nan"), device=cuda)
+    out = torch.empty((B, Hq, D), dtype=torch.bfloat16, device=cuda)
+    runtime.decode_splitk(q.to(cuda), k.to(cuda), v.to(cuda), partials, out, B=B, Hq=Hq, Hkv=Hkv, L=L, D=D,
+                          n_splits=S, dtype="bf16", scale_log2=LOG2E / math.sqrt(D))
+    finish()
+    assert_storage_close(out, decode.decode_reference(q, k, v), 2e-2)
+    m, l, o = decode.decode_partials(q, k, v, S)
+    p = partials.cpu()
+    torch.testing.assert_close(p[..., D] / LOG2E, m, rtol=1e-4, atol=1e-4)     # kernel keeps m in the exp2 domain
+    torch.testing.assert_close(p[..., D + 1], l, rtol=1e-3, atol=1e-4)
+    torch.testing.assert_close(p[..., :D], o, rtol=1e-3, atol=2e-3)
+
+
 def test_combine_with_gather_strides_and_partial_output(cuda, native_lib):
     """The cross-GPU merge: per-rank partials laid out [rank, rows, D+2] merge to the same answer."""
     from neptune_mlir import runtime
