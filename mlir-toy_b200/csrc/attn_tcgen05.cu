@@ -39,6 +39,7 @@ using namespace sm100;
 
 constexpr int kBM = 128;            // query rows per CTA
 constexpr int kBN = 64;             // kv rows per pipeline step
+constexpr int kHeadGroup = 16;      // heads whose tiles are interleaved (tile-major) in the launch order
 constexpr int kD = 128;             // head dimension
 constexpr int kThreads = 192;
 constexpr int kQBytes = kBM * kD * 2;           // 32 KB: two 64-column boxes of 16 KB
@@ -91,7 +92,7 @@ template <int DT, int POLY>
 __global__ void __launch_bounds__(kThreads, 2)
 attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                         const __grid_constant__ CUtensorMap tm_v, uint16_t *__restrict__ out, int Sq, int Skv,
-                        int n_qtiles, float scale_log2, int causal, int *status) {
+                        int n_qtiles, int n_units, int group, float scale_log2, int causal, int *status) {
   extern __shared__ unsigned char smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -103,9 +104,14 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  // tile -> (head, query tile): consecutive CTAs share a head; causal tiles longest first
-  const int bh = blockIdx.x / n_qtiles;
-  const int qi = blockIdx.x % n_qtiles;
+  // tile -> (head, query tile).  Heads are taken in groups of `group`; inside a group the order is tile-major
+  // with the longest causal tiles first, so that the CTAs in flight at any moment belong to few heads (their
+  // K/V stay in L2) while the last CTAs of a group, and of the launch, are the shortest ones.
+  const int per_group = group * n_qtiles;
+  const int grp = blockIdx.x / per_group, rem = blockIdx.x % per_group;
+  const int heads_here = min(group, n_units - grp * group);
+  const int qi = rem / heads_here;
+  const int bh = grp * group + rem % heads_here;
   const int qt = causal ? (n_qtiles - 1 - qi) : qi;
   const int kv_off = Skv - Sq;                                    // causal diagonal offset (multiple of 128)
   const int last_col = qt * kBM + kv_off + kBM - 1;               // last kv column any row of the tile sees
@@ -444,8 +450,13 @@ int launch_tc(const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &t
   NB200_CHECK_CUDA(cudaFuncSetAttribute(attn_fwd_tcgen05_kernel<DT, POLY>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                         cudaSharedmemCarveoutMaxShared));
   const int n_qtiles = Sq / kBM;
+  static const int group_env = [] {
+    const char *e = getenv("NB200_ATTN_GROUP");
+    return e ? atoi(e) : 0;
+  }();
+  const int group = min(BH, group_env > 0 ? group_env : kHeadGroup);
   attn_fwd_tcgen05_kernel<DT, POLY><<<dim3(BH * n_qtiles), dim3(kThreads), kSmemBytes, st>>>(
-      tq, tk, tv, static_cast<uint16_t *>(out), Sq, Skv, n_qtiles, scale_log2, causal, status);
+      tq, tk, tv, static_cast<uint16_t *>(out), Sq, Skv, n_qtiles, BH, group, scale_log2, causal, status);
   NB200_CHECK_CUDA(cudaGetLastError());
   return NB200_OK;
 }
