@@ -3,17 +3,22 @@
 // One CTA computes a tile of 128 query rows of one (batch, head) against the KV sequence in blocks
 // of 64 rows, with the online softmax of the HTile program
 // (tests/data/flash_attention_htile.mlir:40-143 of the reference) kept in the exp2 domain.  The
-// three stages of a block -- S = Q K^T, softmax, O += P V -- form a software pipeline that is two
-// blocks deep, so the tensor pipe computes S(j+1) and S(j+2) while the softmax warps work on S(j):
+// three stages of a block -- S = Q K^T, softmax, O += P V -- run as a software pipeline, each stage on
+// warps of its own that meet only at mbarriers:
 //
-//   warp 4 (one lane)   TMA producer: Q once, then K(j), V(j) into two 16 KB buffers each
-//                       (128-byte swizzled), re-armed when the MMA that read a buffer has retired
-//   warp 5 (one lane)   MMA issuer, operand descriptors built once: S_b = Q K(j)^T
-//                       (8 x tcgen05.mma 128x64x16, both operands in smem) into one of two
-//                       64-column TMEM buffers b = j mod 2, issued two blocks ahead;
-//                       O += P_b V(j) (4 x tcgen05.mma 128x128x16) with P read from TMEM, where it
-//                       overwrites S_b in place as packed 16-bit, and V as an MN-major smem
-//                       operand; the accumulator O lives in TMEM columns 128..255
+//   warp 4, warp 7      TMA producers (one lane each): Q once and K(j); V(j).  Two 16 KB buffers per
+//   (one lane each)     operand (128-byte swizzled), re-armed when the MMA that read a buffer has
+//                       retired.  Separate threads because K(j+1) is wanted a whole block before
+//                       V(j+1): one thread waiting for the V buffer would hold the K load back
+//   warp 5 (one lane)   QK issuer, operand descriptors built once: S = Q K(j)^T (8 x tcgen05.mma
+//                       128x64x16, both operands in smem) into TMEM columns 0..63.  The softmax warps
+//                       copy S(j-1) into registers first thing and release the buffer, so S(j) is
+//                       computed while they work on block j-1
+//   warp 6 (one lane)   PV issuer: O += P_b V(j) (4 x tcgen05.mma 128x128x16) with P read from TMEM
+//                       (two buffers of 32 columns, packed 16-bit) and V as an MN-major smem operand;
+//                       the accumulator O lives in TMEM columns 128..255.  A thread of its own, so
+//                       that a product is issued the moment P arrives instead of queueing behind
+//                       the score products of a later block
 //   warps 0-3           softmax: thread r owns row r (TMEM lane r), so row max and row sum need no
 //                       cross-thread traffic; the 64 scores are read from TMEM once into registers
 //                       (three-input maxima, packed f32x2 scale/sum, exp2, pack to 16 bit).
@@ -27,8 +32,6 @@
 // records a code in the status words and unwinds.
 #include <cuda.h>
 
-#include <cstdlib>
-
 #include "nb200_common.cuh"
 #include "sm100_primitives.cuh"
 
@@ -41,19 +44,19 @@ constexpr int kBM = 128;            // query rows per CTA
 constexpr int kBN = 64;             // kv rows per pipeline step
 constexpr int kHeadGroup = 16;      // heads whose tiles are interleaved (tile-major) in the launch order
 constexpr int kD = 128;             // head dimension
-constexpr int kThreads = 192;
+constexpr int kThreads = 256;       // 4 softmax warps, K producer, QK issuer, PV issuer, V producer
 constexpr int kQBytes = kBM * kD * 2;           // 32 KB: two 64-column boxes of 16 KB
 constexpr int kQBox = kQBytes / 2;
 constexpr int kKVBytes = kBN * kD * 2;          // 16 KB: two 64-column boxes of 8 KB
 constexpr int kKVBox = kKVBytes / 2;
-constexpr int kTmemCols = 256;                  // S0 | S1 | O
+constexpr int kTmemCols = 256;                  // S (64) | P0 (32) | P1 (32) | O (128)
 constexpr int kSmemBytes = kQBytes + 4 * kKVBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
 constexpr float kRescaleThreshold = 8.0f;       // log2 units
 
 enum : int { kErrProducer = 1, kErrMma = 2, kErrSoftmax = 3, kErrEpilogue = 4 };
 
 struct Barriers {
-  uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full[2], pv_done, o_full;
+  uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full, s_free, p_full[2], pv_done[2], o_full;
   uint32_t tmem_base;
   int abort_flag;
   int skip;
@@ -67,28 +70,7 @@ __device__ __forceinline__ void report(int *status, int code, int detail) {
   }
 }
 
-// 2^x for a packed pair on the FMA pipe: round-to-nearest split x = n + f with the 1.5*2^23 trick,
-// degree-3 minimax polynomial for 2^f on [-0.5, 0.5] (max relative error 7.5e-5, far below the
-// rounding of P to 16 bits), exponent added to the bits.  x is clamped at -126 (result ~1e-38).
-__device__ __forceinline__ float2 ex2_poly_pair(uint64_t x2) {
-  float2 x = f2_unpack(x2);
-  x.x = fmaxf(x.x, -126.f);
-  x.y = fmaxf(x.y, -126.f);
-  const uint64_t xc = f2_pack(x.x, x.y);
-  const uint64_t magic = f2_pack(12582912.f, 12582912.f), neg_magic = f2_pack(-12582912.f, -12582912.f);
-  const uint64_t t2 = f2_add(xc, magic);                                  // low mantissa bits = round(x)
-  const uint64_t f2 = f2_fma(f2_add(t2, neg_magic), f2_pack(-1.f, -1.f), xc);  // x - round(x)
-  uint64_t r2 = f2_fma(f2, f2_pack(0.05517164617776871f, 0.05517164617776871f),
-                       f2_pack(0.2426111251115799f, 0.2426111251115799f));
-  r2 = f2_fma(r2, f2, f2_pack(0.6932609677314758f, 0.6932609677314758f));
-  r2 = f2_fma(r2, f2, f2_pack(0.9999280571937561f, 0.9999280571937561f));
-  const float2 r = f2_unpack(r2), t = f2_unpack(t2);
-  return make_float2(__int_as_float(__float_as_int(r.x) + (__float_as_int(t.x) << 23)),
-                     __int_as_float(__float_as_int(r.y) + (__float_as_int(t.y) << 23)));
-}
-
-// POLY = how many of every 8 pairs take their exponential on the FMA pipe instead of the MUFU.
-template <int DT, int POLY>
+template <int DT>
 __global__ void __launch_bounds__(kThreads, 2)
 attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                         const __grid_constant__ CUtensorMap tm_v, uint16_t *__restrict__ out, int Sq, int Skv,
@@ -128,11 +110,12 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
       mbar_init(smem_u32(&bars->k_empty[b]), 1);
       mbar_init(smem_u32(&bars->v_full[b]), 1);
       mbar_init(smem_u32(&bars->v_empty[b]), 1);
-      mbar_init(smem_u32(&bars->s_full[b]), 1);
       mbar_init(smem_u32(&bars->p_full[b]), 128);
+      mbar_init(smem_u32(&bars->pv_done[b]), 1);
     }
-    mbar_init(smem_u32(&bars->pv_done), 1);
     mbar_init(smem_u32(&bars->o_full), 1);
+    mbar_init(smem_u32(&bars->s_full), 1);
+    mbar_init(smem_u32(&bars->s_free), 128);
     fence_barrier_init();
     fence_proxy_async_smem();
   }
@@ -152,46 +135,67 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = bars->tmem_base;
-  const uint32_t tS0 = tmem, tO = tmem + 2 * kBN;  // S buffer b is at + b * kBN columns
+  const uint32_t tS = tmem, tP0 = tmem + kBN, tO = tmem + 2 * kBN;  // P buffer b is at tP0 + b * kBN / 2 columns
 
   const uint32_t b_q_full = smem_u32(&bars->q_full), b_k_full = smem_u32(&bars->k_full[0]),
                  b_k_empty = smem_u32(&bars->k_empty[0]), b_v_full = smem_u32(&bars->v_full[0]),
-                 b_v_empty = smem_u32(&bars->v_empty[0]), b_s_full = smem_u32(&bars->s_full[0]),
-                 b_p_full = smem_u32(&bars->p_full[0]), b_pv_done = smem_u32(&bars->pv_done),
+                 b_v_empty = smem_u32(&bars->v_empty[0]), b_s_full = smem_u32(&bars->s_full), b_s_free = smem_u32(&bars->s_free),
+                 b_p_full = smem_u32(&bars->p_full[0]), b_pv_done = smem_u32(&bars->pv_done[0]),
                  b_o_full = smem_u32(&bars->o_full);  // buffer b of a pair is at +8*b
 
   if (warp == 4) {
-    // ================================ TMA producer ================================
+    // ================================ TMA producer: Q and K ================================
+    // K and V have a producer thread each: K(j+1) is wanted a whole block before V(j+1), and a single
+    // thread that waits for the V buffer first would hold the K load back.
     if (lane == 0) {
       mbar_arrive_expect_tx(b_q_full, kQBytes);
       tma_load_2d(sQ, &tm_q, 0, q_row0, b_q_full);
       tma_load_2d(sQ + kQBox, &tm_q, 64, q_row0, b_q_full);
-      int issued_k = 0, issued_v = 0;
+      int issued = 0;
       bool ok = true;
       for (int j = 0; j < nblk && ok; ++j) {
         const int b = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        ok = mbar_wait(b_k_empty + 8 * b, ph ^ 1, abort_flag);
+        ok = mbar_wait(b_k_empty + 8 * b, ((j >> 1) & 1) ^ 1, abort_flag);
         if (!ok) { report(status, kErrProducer, 2 * j); break; }
         mbar_arrive_expect_tx(b_k_full + 8 * b, kKVBytes);
         tma_load_2d(sK0 + b * kKVBytes, &tm_k, 0, kv_row0 + j * kBN, b_k_full + 8 * b);
         tma_load_2d(sK0 + b * kKVBytes + kKVBox, &tm_k, 64, kv_row0 + j * kBN, b_k_full + 8 * b);
-        ++issued_k;
-        ok = mbar_wait(b_v_empty + 8 * b, ph ^ 1, abort_flag);
-        if (!ok) { report(status, kErrProducer, 2 * j + 1); break; }
-        mbar_arrive_expect_tx(b_v_full + 8 * b, kKVBytes);
-        tma_load_2d(sV0 + b * kKVBytes, &tm_v, 0, kv_row0 + j * kBN, b_v_full + 8 * b);
-        tma_load_2d(sV0 + b * kKVBytes + kKVBox, &tm_v, 64, kv_row0 + j * kBN, b_v_full + 8 * b);
-        ++issued_v;
+        ++issued;
       }
       if (!ok) {
         // Unwinding: let the copies already in flight land before the CTA's shared memory goes away.
         mbar_wait(b_q_full, 0, abort_flag);
         for (int spin = 0; spin < 100000; ++spin) {
           bool done = true;
-          for (int n = 0; n < 2; ++n) {  // the last two loads of each kind
-            const int jk = issued_k - 1 - n, jv = issued_v - 1 - n;
+          for (int n = 0; n < 2; ++n) {  // the last two loads
+            const int jk = issued - 1 - n;
             if (jk >= 0) done = done && mbar_try_wait(b_k_full + 8 * (jk & 1), (jk >> 1) & 1);
+          }
+          if (done) break;
+          __nanosleep(100);
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 7) {
+    // ================================ TMA producer: V ======================================
+    if (lane == 0) {
+      int issued = 0;
+      bool ok = true;
+      for (int j = 0; j < nblk && ok; ++j) {
+        const int b = j & 1;
+        ok = mbar_wait(b_v_empty + 8 * b, ((j >> 1) & 1) ^ 1, abort_flag);
+        if (!ok) { report(status, kErrProducer, 2 * j + 1); break; }
+        mbar_arrive_expect_tx(b_v_full + 8 * b, kKVBytes);
+        tma_load_2d(sV0 + b * kKVBytes, &tm_v, 0, kv_row0 + j * kBN, b_v_full + 8 * b);
+        tma_load_2d(sV0 + b * kKVBytes + kKVBox, &tm_v, 64, kv_row0 + j * kBN, b_v_full + 8 * b);
+        ++issued;
+      }
+      if (!ok) {
+        for (int spin = 0; spin < 100000; ++spin) {
+          bool done = true;
+          for (int n = 0; n < 2; ++n) {
+            const int jv = issued - 1 - n;
             if (jv >= 0) done = done && mbar_try_wait(b_v_full + 8 * (jv & 1), (jv >> 1) & 1);
           }
           if (done) break;
@@ -201,14 +205,16 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
     }
     __syncwarp();
   } else if (warp == 5) {
-    // ================================ MMA issuer ==================================
+    // ================================ QK issuer ===================================
+    // S = Q K(j)^T.  The softmax warps copy S(j-1) into registers first thing and release the buffer,
+    // so S(j) is computed while they work on block j-1.  A thread of its own, so that the score
+    // products keep flowing while the other issuer waits for the softmax warps.
     if (lane == 0) {
       constexpr int fmt = (DT == NB200_BF16) ? 1 : 0;
       constexpr uint32_t idesc_qk = umma_idesc_f16(fmt, 0, kBM, kBN);
-      constexpr uint32_t idesc_pv = umma_idesc_f16(fmt, 1, kBM, kD);
       // Operand descriptors never change: build them once, so that issuing an MMA is a couple of
       // instructions (building one per MMA costs ~90 cycles of scalar work and starves the pipe).
-      uint64_t dq[kD / 16], dk[2][kD / 16], dv[2][kBN / 16];
+      uint64_t dq[kD / 16], dk[2][kD / 16];
 #pragma unroll
       for (int kk = 0; kk < kD / 16; ++kk) {
         // 16 elements of the reduction per MMA = 32 bytes inside the 128-byte swizzled row
@@ -216,34 +222,42 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
 #pragma unroll
         for (int b = 0; b < 2; ++b) dk[b][kk] = umma_desc_sw128(sK0 + b * kKVBytes + (kk >> 2) * kKVBox + (kk & 3) * 32, 16, 1024);
       }
+      bool ok = mbar_wait(b_q_full, 0, abort_flag);
+      if (!ok) report(status, kErrMma, -1);
+      for (int j = 0; j < nblk && ok; ++j) {
+        const int b = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        ok = mbar_wait(b_k_full + 8 * b, ph, abort_flag);
+        if (!ok) { report(status, kErrMma, 3 * j); break; }
+        if (j >= 1) {
+          ok = mbar_wait(b_s_free, (j - 1) & 1, abort_flag);   // the softmax warps hold S(j-1) in registers
+          if (!ok) { report(status, kErrMma, 3 * j + 1); break; }
+        }
+        tc_fence_after();
+        if (b == 0) {
+#pragma unroll
+          for (int kk = 0; kk < kD / 16; ++kk) umma_ss(tS, dq[kk], dk[0][kk], idesc_qk, kk > 0);
+        } else {
+#pragma unroll
+          for (int kk = 0; kk < kD / 16; ++kk) umma_ss(tS, dq[kk], dk[1][kk], idesc_qk, kk > 0);
+        }
+        umma_commit(b_k_empty + 8 * b);
+        umma_commit(b_s_full);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 6) {
+    // ================================ PV issuer ===================================
+    if (lane == 0) {
+      constexpr int fmt = (DT == NB200_BF16) ? 1 : 0;
+      constexpr uint32_t idesc_pv = umma_idesc_f16(fmt, 1, kBM, kD);
+      uint64_t dv[2][kBN / 16];
 #pragma unroll
       for (int b = 0; b < 2; ++b)
 #pragma unroll
         for (int kk = 0; kk < kBN / 16; ++kk)  // V: 16 kv rows = 2 KB; the two 64-column blocks are 8 KB apart
           dv[b][kk] = umma_desc_sw128(sV0 + b * kKVBytes + kk * 2048, kKVBox, 1024);
-
-      bool ok = mbar_wait(b_q_full, 0, abort_flag);
-      if (!ok) report(status, kErrMma, -1);
-
-      // S_b = Q K(jj)^T for block jj into buffer b = jj & 1
-      auto issue_qk = [&](int jj) -> bool {
-        const int b = jj & 1;
-        if (!mbar_wait(b_k_full + 8 * b, (jj >> 1) & 1, abort_flag)) { report(status, kErrMma, 3 * jj); return false; }
-        tc_fence_after();
-        if (b == 0) {
-#pragma unroll
-          for (int kk = 0; kk < kD / 16; ++kk) umma_ss(tS0, dq[kk], dk[0][kk], idesc_qk, kk > 0);
-        } else {
-#pragma unroll
-          for (int kk = 0; kk < kD / 16; ++kk) umma_ss(tS0 + kBN, dq[kk], dk[1][kk], idesc_qk, kk > 0);
-        }
-        umma_commit(b_k_empty + 8 * b);
-        umma_commit(b_s_full + 8 * b);
-        return true;
-      };
-
-      if (ok) ok = issue_qk(0);
-      if (ok && nblk > 1) ok = issue_qk(1);
+      bool ok = true;
       for (int j = 0; j < nblk && ok; ++j) {
         const int b = j & 1;
         const uint32_t ph = (j >> 1) & 1;
@@ -256,15 +270,13 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         const uint32_t acc0 = j > 0 ? 1u : 0u;
         if (b == 0) {
 #pragma unroll
-          for (int kk = 0; kk < kBN / 16; ++kk) umma_ts(tO, tS0 + kk * 8, dv[0][kk], idesc_pv, kk > 0 ? 1u : acc0);
+          for (int kk = 0; kk < kBN / 16; ++kk) umma_ts(tO, tP0 + kk * 8, dv[0][kk], idesc_pv, kk > 0 ? 1u : acc0);
         } else {
 #pragma unroll
-          for (int kk = 0; kk < kBN / 16; ++kk) umma_ts(tO, tS0 + kBN + kk * 8, dv[1][kk], idesc_pv, kk > 0 ? 1u : acc0);
+          for (int kk = 0; kk < kBN / 16; ++kk) umma_ts(tO, tP0 + kBN / 2 + kk * 8, dv[1][kk], idesc_pv, kk > 0 ? 1u : acc0);
         }
         umma_commit(b_v_empty + 8 * b);
-        umma_commit(b_pv_done);
-        // S_b is free again (MMAs execute in issue order): start block j+2 into it
-        if (j + 2 < nblk) ok = issue_qk(j + 2);
+        umma_commit(b_pv_done + 8 * b);   // P_b is free again, and O holds every product up to block j
       }
       if (ok) umma_commit(b_o_full);
     }
@@ -278,16 +290,18 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
     for (int j = 0; j < nblk; ++j) {
       const int b = j & 1;
       // warp-uniform outcome: the TMEM accesses below are warp-collective
-      ok = __all_sync(0xffffffffu, mbar_wait(b_s_full + 8 * b, (j >> 1) & 1, abort_flag));
+      ok = __all_sync(0xffffffffu, mbar_wait(b_s_full, j & 1, abort_flag));
       if (!ok) { report(status, kErrSoftmax, j); break; }
       tc_fence_after();
-      const uint32_t tSb = tS0 + b * kBN + lane_addr;
+      const uint32_t tPb = tP0 + b * (kBN / 2) + lane_addr;
 
-      // ---- the 64 scores of this row into registers (one TMEM read) ----
+      // ---- the 64 scores of this row into registers (one TMEM read); S is then free for block j+1 ----
       uint32_t v[kBN];
-      tmem_ld32p(tSb, v);
-      tmem_ld32p(tSb + 32, v + 32);
+      tmem_ld32p(tS + lane_addr, v);
+      tmem_ld32p(tS + lane_addr + 32, v + 32);
       tmem_wait_ld();
+      tc_fence_before();
+      mbar_arrive(b_s_free);
       // causal: column c of block j is visible to row r iff j*64 + c <= qt*128 + kv_off + r
       const int vis = causal ? (qt * kBM + kv_off + r - j * kBN) : kBN;  // columns 0..vis are visible
       if (vis < kBN - 1) {
@@ -315,9 +329,9 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
       } else {
         const bool need = m_blk > m_used + kRescaleThreshold;
         if (__any_sync(0xffffffffu, need)) {
-          // O must hold every product up to block j-1 and none may be in flight.  S(j) was issued
-          // after PV(j-2), so only PV(j-1) can be outstanding: its completion is phase j-1 of pv_done.
-          ok = __all_sync(0xffffffffu, mbar_wait(b_pv_done, (j - 1) & 1, abort_flag));
+          // O must hold every product up to block j-1 and none may be in flight: wait for PV(j-1)
+          // (the products before it were issued earlier by the same thread and complete in order).
+          ok = __all_sync(0xffffffffu, mbar_wait(b_pv_done + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1, abort_flag));
           if (!ok) { report(status, kErrSoftmax, 1000 + j); break; }
           tc_fence_after();
           const float f = need ? ex2(m_used - m_blk) : 1.f;
@@ -336,7 +350,12 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         }
       }
 
-      // ---- p = 2^(s*scale - m) on packed pairs, row sum, pack to 16 bit, write P over S ----
+      // ---- p = 2^(s*scale - m) on packed pairs, row sum, pack to 16 bit, write P_b ----
+      if (j >= 2) {  // PV(j-2) read P_b; it completed long ago, this only makes the order formal
+        ok = __all_sync(0xffffffffu, mbar_wait(b_pv_done + 8 * b, ((j - 2) >> 1) & 1, abort_flag));
+        if (!ok) { report(status, kErrSoftmax, 2000 + j); break; }
+        tc_fence_after();
+      }
       const uint64_t c2 = f2_pack(scale_log2, scale_log2), nm2 = f2_pack(-m_used, -m_used);
       uint64_t lsum2 = f2_pack(0.f, 0.f);
 #pragma unroll
@@ -346,20 +365,12 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         for (int i = 0; i < 16; ++i) {
           const uint64_t x2 = f2_fma(
               f2_pack(__uint_as_float(v[c * 32 + 2 * i]), __uint_as_float(v[c * 32 + 2 * i + 1])), c2, nm2);
-          float p0, p1;
-          if ((i & 7) < POLY) {
-            const float2 pp = ex2_poly_pair(x2);
-            p0 = pp.x;
-            p1 = pp.y;
-          } else {
-            const float2 x = f2_unpack(x2);
-            p0 = ex2(x.x);
-            p1 = ex2(x.y);
-          }
+          const float2 x = f2_unpack(x2);
+          const float p0 = ex2(x.x), p1 = ex2(x.y);
           lsum2 = f2_add(lsum2, f2_pack(p0, p1));
           pk[i] = pack2<DT>(p0, p1);
         }
-        tmem_st16(tSb + c * 16, pk);
+        tmem_st16(tPb + c * 16, pk);
       }
       {
         const float2 ls = f2_unpack(lsum2);
@@ -440,22 +451,18 @@ int make_tile_map(CUtensorMap *tm, const void *ptr, long long rows, int dtype, i
   return NB200_OK;
 }
 
-template <int DT, int POLY>
+template <int DT>
 int launch_tc(const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv, void *out, int BH, int Sq,
               int Skv, float scale_log2, int causal, int *status, cudaStream_t st) {
   // per-device attribute: set on every call so that any current device is covered
-  NB200_CHECK_CUDA(cudaFuncSetAttribute(attn_fwd_tcgen05_kernel<DT, POLY>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  NB200_CHECK_CUDA(cudaFuncSetAttribute(attn_fwd_tcgen05_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         kSmemBytes));
   // two CTAs of ~97 KB must fit: ask for the largest shared-memory carve-out
-  NB200_CHECK_CUDA(cudaFuncSetAttribute(attn_fwd_tcgen05_kernel<DT, POLY>, cudaFuncAttributePreferredSharedMemoryCarveout,
+  NB200_CHECK_CUDA(cudaFuncSetAttribute(attn_fwd_tcgen05_kernel<DT>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                         cudaSharedmemCarveoutMaxShared));
   const int n_qtiles = Sq / kBM;
-  static const int group_env = [] {
-    const char *e = getenv("NB200_ATTN_GROUP");
-    return e ? atoi(e) : 0;
-  }();
-  const int group = min(BH, group_env > 0 ? group_env : kHeadGroup);
-  attn_fwd_tcgen05_kernel<DT, POLY><<<dim3(BH * n_qtiles), dim3(kThreads), kSmemBytes, st>>>(
+  const int group = min(BH, kHeadGroup);
+  attn_fwd_tcgen05_kernel<DT><<<dim3(BH * n_qtiles), dim3(kThreads), kSmemBytes, st>>>(
       tq, tk, tv, static_cast<uint16_t *>(out), Sq, Skv, n_qtiles, BH, group, scale_log2, causal, status);
   NB200_CHECK_CUDA(cudaGetLastError());
   return NB200_OK;
@@ -492,24 +499,7 @@ extern "C" int nb200_attn_fwd(const void *q, const void *k, const void *v, void 
   if ((rc = make_tile_map(&tq, q, (long long)B * H * Sq, dtype, kBM)) != NB200_OK) return rc;
   if ((rc = make_tile_map(&tk, k, (long long)B * H * Skv, dtype, kBN)) != NB200_OK) return rc;
   if ((rc = make_tile_map(&tv, v, (long long)B * H * Skv, dtype, kBN)) != NB200_OK) return rc;
-  static const int poly = [] {
-    const char *e = getenv("NB200_ATTN_POLY");
-    return e ? atoi(e) : 0;
-  }();
-#define NB200_TC(DTV, PV) launch_tc<DTV, PV>(tq, tk, tv, out, B * H, Sq, Skv, scale_log2, causal, status, st)
-  if (dtype == NB200_BF16) {
-    switch (poly) {
-      case 2: return NB200_TC(NB200_BF16, 2);
-      case 3: return NB200_TC(NB200_BF16, 3);
-      case 4: return NB200_TC(NB200_BF16, 4);
-      default: return NB200_TC(NB200_BF16, 0);
-    }
-  }
-  switch (poly) {
-    case 2: return NB200_TC(NB200_F16, 2);
-    case 3: return NB200_TC(NB200_F16, 3);
-    case 4: return NB200_TC(NB200_F16, 4);
-    default: return NB200_TC(NB200_F16, 0);
-  }
-#undef NB200_TC
+  if (dtype == NB200_BF16)
+    return launch_tc<NB200_BF16>(tq, tk, tv, out, B * H, Sq, Skv, scale_log2, causal, status, st);
+  return launch_tc<NB200_F16>(tq, tk, tv, out, B * H, Sq, Skv, scale_log2, causal, status, st);
 }
