@@ -45,14 +45,14 @@ constexpr int kBCBytes = kQ * kN * 2;      // 32 KB: two 64-column boxes of 16 K
 constexpr int kBCBox = kBCBytes / 2;
 constexpr int kXBytes = kQ * kP * 2;       // 16 KB: one box
 constexpr int kTileBytes = 2 * kBCBytes + kXBytes;
-constexpr int kSsdSmem = 2 * kBCBytes + 2 * kXBytes + 4 * kQ * 4 /*lb*/ + 256 /*barriers*/;
+constexpr int kSsdSmem = 2 * kBCBytes + 2 * kXBytes + 4 * 2 * kQ * 4 /*lb, cf*/ + 256 /*barriers*/;
 constexpr int kSsdTmemCols = 256;
 constexpr float kLog2e = 1.4426950408889634f;
 
 enum : int { kErrSsdProducer = 11, kErrSsdMma = 12, kErrSsdCompute = 13, kErrSsdAlign = 15 };
 
 struct SsdBarriers {
-  uint64_t c_full, b_full, x_full, z_done, y_staged, e1a, inter_done, e1b, g_ready, m_ready, y_ready;
+  uint64_t c_full, b_full, x_full, z_done, y_staged, y_free, e1a, inter_done, e1b, g_ready, m_ready, y_ready;
   uint32_t tmem_base;
   int abort_flag;
   int skip;
@@ -86,10 +86,12 @@ ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
     if (threadIdx.x == 0) ssd_report(status, kErrSsdAlign, static_cast<int>(base));
     return;
   }
-  const uint32_t sB = base, sC = base + kBCBytes, sX = base + 2 * kBCBytes, sXs = sX + kXBytes;
-  unsigned char *pC = smem + kBCBytes, *pX = smem + 2 * kBCBytes, *pXs = pX + kXBytes;
-  float *lb_all = reinterpret_cast<float *>(smem + 2 * kBCBytes + 2 * kXBytes);  // [4 warps][128]
-  SsdBarriers *bars = reinterpret_cast<SsdBarriers *>(smem + 2 * kBCBytes + 2 * kXBytes + 4 * kQ * 4);
+  // Two 16 KB buffers U0, U1 change roles every step: in step s, U[s&1] holds x(s) and later the finished Y(s),
+  // U[(s+1)&1] holds the 16-bit copy of the incoming state, then w*x(s), then (loaded ahead) x(s+1).
+  const uint32_t sB = base, sC = base + kBCBytes, sU = base + 2 * kBCBytes;
+  unsigned char *pU = smem + 2 * kBCBytes;
+  float *lb_all = reinterpret_cast<float *>(smem + 2 * kBCBytes + 2 * kXBytes);  // [4 warps][lb 128 | cf 128]
+  SsdBarriers *bars = reinterpret_cast<SsdBarriers *>(smem + 2 * kBCBytes + 2 * kXBytes + 4 * 2 * kQ * 4);
   volatile int *abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -105,6 +107,7 @@ ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
     mbar_init(smem_u32(&bars->x_full), 1);
     mbar_init(smem_u32(&bars->z_done), 1);
     mbar_init(smem_u32(&bars->y_staged), 128);
+    mbar_init(smem_u32(&bars->y_free), 1);
     mbar_init(smem_u32(&bars->e1a), 128);
     mbar_init(smem_u32(&bars->inter_done), 1);
     mbar_init(smem_u32(&bars->e1b), 128);
@@ -135,7 +138,7 @@ ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
 
   const uint32_t b_c_full = smem_u32(&bars->c_full), b_b_full = smem_u32(&bars->b_full),
                  b_x_full = smem_u32(&bars->x_full), b_z_done = smem_u32(&bars->z_done),
-                 b_y_staged = smem_u32(&bars->y_staged), b_e1a = smem_u32(&bars->e1a), b_inter_done = smem_u32(&bars->inter_done),
+                 b_y_staged = smem_u32(&bars->y_staged), b_y_free = smem_u32(&bars->y_free), b_e1a = smem_u32(&bars->e1a), b_inter_done = smem_u32(&bars->inter_done),
                  b_e1b = smem_u32(&bars->e1b), b_g_ready = smem_u32(&bars->g_ready),
                  b_m_ready = smem_u32(&bars->m_ready), b_y_ready = smem_u32(&bars->y_ready);
 
@@ -160,7 +163,7 @@ ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       };
       auto load_x = [&](int s) {
         mbar_arrive_expect_tx(b_x_full, kXBytes);
-        tma_load_2d(sX, &tm_x, h * kP, b * L + s * kQ, b_x_full);
+        tma_load_2d(sU + (s & 1) * kXBytes, &tm_x, h * kP, b * L + s * kQ, b_x_full);
         ++issued_x;
       };
       load_c(0);
@@ -169,7 +172,8 @@ ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       for (int s = 0; s < nsteps; ++s) {
         const uint32_t ph = s & 1;
         const bool more = s + 1 < nsteps;
-        // the buffers of step s become free in this order: C (after G and C.S_in), B (after the state update), x (after Y)
+        // the buffers of step s become free in this order: C (after G and C.S_in); B and the buffer of w*x
+        // (after the state update), which takes x(s+1) at once so that the load has most of a step to arrive
         if (more) {
           ok = mbar_wait(b_inter_done, ph, abort_flag);
           if (!ok) { ssd_report(status, kErrSsdProducer, 4 * s); break; }
@@ -177,15 +181,17 @@ ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
           ok = mbar_wait(b_z_done, ph, abort_flag);
           if (!ok) { ssd_report(status, kErrSsdProducer, 4 * s + 1); break; }
           load_b(s + 1);
+          load_x(s + 1);
         }
-        // the finished Y tile sits where x was: store it, then refill the buffer with the next x
+        // the finished Y tile sits where x(s) was: store it; the next step's state copy may overwrite the
+        // buffer once the store has read it
         ok = mbar_wait(b_y_staged, ph, abort_flag);
         if (!ok) { ssd_report(status, kErrSsdProducer, 4 * s + 2); break; }
-        tma_store_2d(&tm_y, sX, h * kP, b * L + s * kQ);
+        tma_store_2d(&tm_y, sU + (s & 1) * kXBytes, h * kP, b * L + s * kQ);
         tma_store_commit();
         if (more) {
           tma_store_wait_read();
-          load_x(s + 1);
+          mbar_arrive(b_y_free);
         }
       }
       tma_store_wait_all();
@@ -208,7 +214,7 @@ ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       constexpr uint32_t id_g = umma_idesc_f16_ab(fmt, 0, 0, kQ, kQ);       // A: C, B: B, both K-major
       constexpr uint32_t id_z = umma_idesc_f16_ab(fmt, 1, 1, kN, kP);       // A: B^T (MN-major), B: w x (MN-major)
       constexpr uint32_t id_m2 = umma_idesc_f16_ab(fmt, 0, 1, kQ, kP);      // A: TMEM, B: x (MN-major)
-      uint64_t dC[8], dB[8], dBt[8], dX[8], dXs[8];
+      uint64_t dC[8], dB[8], dBt[8], dU[2][8];
 #pragma unroll
       for (int kk = 0; kk < 8; ++kk) {
         const uint32_t off = (kk >> 2) * kBCBox + (kk & 3) * 32;  // 16 elements of n per MMA inside the swizzled row
@@ -216,8 +222,8 @@ ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
         dB[kk] = umma_desc_sw128(sB + off, 16, 1024);
         // reduction over rows (time steps / state rows): 16 rows = 2 KB per MMA; 64-column blocks 16 KB apart
         dBt[kk] = umma_desc_sw128(sB + kk * 2048, kBCBox, 1024);
-        dX[kk] = umma_desc_sw128(sX + kk * 2048, kXBytes, 1024);
-        dXs[kk] = umma_desc_sw128(sXs + kk * 2048, kXBytes, 1024);
+        dU[0][kk] = umma_desc_sw128(sU + kk * 2048, kXBytes, 1024);
+        dU[1][kk] = umma_desc_sw128(sU + kXBytes + kk * 2048, kXBytes, 1024);
       }
       bool ok = true;
       for (int s = 0; s < nsteps && ok; ++s) {
@@ -234,21 +240,21 @@ ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
         tc_fence_after();
         // Y = C . S_in      (S_in sits in the buffer that later holds w*x; rows are scaled by e^cum_i afterwards)
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) umma_ss(tY, dC[kk], dXs[kk], id_inter, kk > 0);
+        for (int kk = 0; kk < 8; ++kk) umma_ss(tY, dC[kk], (s & 1) ? dU[0][kk] : dU[1][kk], id_inter, kk > 0);
         umma_commit(b_inter_done);   // also: the C tile is free
         // S = (e^cum_last S) + B^T . (w x)
         ok = mbar_wait(b_e1b, ph, abort_flag);
         if (!ok) { ssd_report(status, kErrSsdMma, 4 * s + 2); break; }
         tc_fence_after();
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) umma_ss(tS, dBt[kk], dXs[kk], id_z, 1u);
+        for (int kk = 0; kk < 8; ++kk) umma_ss(tS, dBt[kk], (s & 1) ? dU[0][kk] : dU[1][kk], id_z, 1u);
         umma_commit(b_z_done);
         // Y += (G o decay o mask) . x
         ok = mbar_wait(b_x_full, ph, abort_flag) && mbar_wait(b_m_ready, ph, abort_flag);
         if (!ok) { ssd_report(status, kErrSsdMma, 4 * s + 3); break; }
         tc_fence_after();
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) umma_ts(tY, tR + kk * 8, dX[kk], id_m2, 1u);
+        for (int kk = 0; kk < 8; ++kk) umma_ts(tY, tR + kk * 8, (s & 1) ? dU[1][kk] : dU[0][kk], id_m2, 1u);
         umma_commit(b_y_ready);
       }
     }
@@ -257,7 +263,8 @@ ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
     // ================================ element-wise warps ==========================
     const int i = warp * 32 + lane;                           // row of the step == TMEM lane
     const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
-    float *lb = lb_all + warp * kQ;                            // this warp's copy of cum_j - log2(dt_j)
+    float *lb = lb_all + warp * 2 * kQ;                        // this warp's copy of cum_j - log2(dt_j)
+    float *cf = lb + kQ;                                       // and of e^(cum_end(j) - cum_j) dt_j, see prefix
     const float a_log2 = A[h] * kLog2e;
     {  // the state starts at zero
       uint32_t z[32];
@@ -271,17 +278,18 @@ ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
     float dt_next[4];
 #pragma unroll
     for (int e = 0; e < 4; ++e) dt_next[e] = dt[(static_cast<size_t>(b) * L + 4 * lane + e) * H + h];
-    for (int s = 0; s < nsteps; ++s) {
-      const uint32_t ph = s & 1;
-      const size_t row0 = static_cast<size_t>(b) * L + static_cast<size_t>(s) * kQ;
-
-      // ---- prefix sum of dt*A over the 128 rows, every warp for itself: lane l holds rows 4l..4l+3 ----
+    // Prefix sum of dt*A over the 128 rows of step sp, every warp for itself (lane l holds rows 4l..4l+3);
+    // leaves total, cum_i and dt_i of this thread's row and this warp's copy of cum_j - log2(dt_j) in lb.
+    // Depends only on dt, so it runs for step s+1 while the last product of step s is in flight.
+    float total = 0.f, cum_i = 0.f, dt_i = 0.f;
+    float ref0 = 0.f, ref1 = 0.f, ref2 = 0.f;   // cum at the last row of column chunks 0..2 (32 columns each)
+    auto prefix = [&](int sp) {
       float dt4[4], cum4[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) dt4[e] = dt_next[e];
-      if (s + 1 < nsteps) {  // the next step's dt, fetched a whole step ahead
+      if (sp + 1 < nsteps) {  // the dt of the step after, fetched a whole step ahead
 #pragma unroll
-        for (int e = 0; e < 4; ++e) dt_next[e] = dt[(row0 + kQ + 4 * lane + e) * H + h];
+        for (int e = 0; e < 4; ++e) dt_next[e] = dt[(static_cast<size_t>(b) * L + static_cast<size_t>(sp + 1) * kQ + 4 * lane + e) * H + h];
       }
       cum4[0] = dt4[0] * a_log2;
 #pragma unroll
@@ -295,23 +303,45 @@ ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       const float excl = incl - cum4[3];
 #pragma unroll
       for (int e = 0; e < 4; ++e) cum4[e] += excl;
-      const float total = __shfl_sync(0xffffffffu, cum4[3], 31);
-      __syncwarp();  // the previous step's readers of lb are done
-      *reinterpret_cast<float4 *>(lb + 4 * lane) =
+      total = __shfl_sync(0xffffffffu, cum4[3], 31);
+      __syncwarp();  // this warp's readers of the previous step's lb (the decay pass) are done
+      const float4 lbv =
           make_float4(cum4[0] - lg2(dt4[0]), cum4[1] - lg2(dt4[1]), cum4[2] - lg2(dt4[2]), cum4[3] - lg2(dt4[3]));
+      *reinterpret_cast<float4 *>(lb + 4 * lane) = lbv;
+      // Column factors for the chunks left of the diagonal: with r = cum at the last row of the 32-column chunk of j,
+      // e^(cum_i - cum_j) dt_j = e^(cum_i - r) * [e^(r - cum_j) dt_j] and both exponents are <= 0 for every row i
+      // below the chunk, so the decay of such a chunk is one factor per row and one per column instead of an
+      // exponential per element.
+      const float r_own = __shfl_sync(0xffffffffu, cum4[3], lane | 7);
+      *reinterpret_cast<float4 *>(cf + 4 * lane) =
+          make_float4(ex2(r_own - lbv.x), ex2(r_own - lbv.y), ex2(r_own - lbv.z), ex2(r_own - lbv.w));
+      ref0 = __shfl_sync(0xffffffffu, cum4[3], 7);
+      ref1 = __shfl_sync(0xffffffffu, cum4[3], 15);
+      ref2 = __shfl_sync(0xffffffffu, cum4[3], 23);
       __syncwarp();
       // this thread's own row: lane (i mod 32) / 4 ... of this warp's block of 32 rows lives at lane 8*warp + lane/4
       const int src = 8 * warp + (lane >> 2), comp = lane & 3;
-      float cum_i = 0.f, dt_i = 0.f;
+      cum_i = 0.f;
+      dt_i = 0.f;
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const float cv = __shfl_sync(0xffffffffu, cum4[e], src), dv = __shfl_sync(0xffffffffu, dt4[e], src);
         if (comp == e) { cum_i = cv; dt_i = dv; }
       }
 
+    };
+    prefix(0);
+    for (int s = 0; s < nsteps; ++s) {
+      const uint32_t ph = s & 1;
+      unsigned char *pX = pU + (s & 1) * kXBytes, *pXs = pU + ((s & 1) ^ 1) * kXBytes;
+
       // ---- E1a: S_in -> 16 bit in smem; S *= e^cum_last.  (The state is final: the previous step's
       //      y_ready, waited for in E3, was committed after its state update.) ----
       {
+        if (s > 0) {  // the copy goes where Y(s-1) was staged: its store must have read the buffer
+          ok = __all_sync(0xffffffffu, mbar_wait(b_y_free, (s - 1) & 1, abort_flag));
+          if (!ok) { ssd_report(status, kErrSsdCompute, 8 * s + 5); break; }
+        }
         uint32_t sv[kP];
         tmem_ld32p(tS + lane_addr, sv);
         tmem_ld32p(tS + lane_addr + 32, sv + 32);
@@ -365,7 +395,21 @@ ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         uint32_t pk[16];
-        if (c <= warp) {  // warp-uniform: columns beyond this warp's last row are masked for all its rows
+        if (c < warp) {  // a chunk left of the diagonal: every column is visible to every row of this warp
+          uint32_t gv[32];
+          tmem_ld32(tR + lane_addr + c * 32, gv);
+          const float rf = ex2(cum_i - (c == 0 ? ref0 : (c == 1 ? ref1 : ref2)));
+          const uint64_t rf2 = f2_pack(rf, rf);
+          tmem_wait_ld();
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const ulonglong2 c4 = *reinterpret_cast<const ulonglong2 *>(cf + c * 32 + q * 4);
+            const float2 m01 = f2_unpack(f2_mul(f2_mul(f2_pack(__uint_as_float(gv[q * 4]), __uint_as_float(gv[q * 4 + 1])), c4.x), rf2));
+            const float2 m23 = f2_unpack(f2_mul(f2_mul(f2_pack(__uint_as_float(gv[q * 4 + 2]), __uint_as_float(gv[q * 4 + 3])), c4.y), rf2));
+            pk[q * 2] = pack2<DT>(m01.x, m01.y);
+            pk[q * 2 + 1] = pack2<DT>(m23.x, m23.y);
+          }
+        } else if (c == warp) {  // the diagonal chunk: exponent and mask per element
           uint32_t gv[32];
           tmem_ld32(tR + lane_addr + c * 32, gv);
           tmem_wait_ld();
@@ -403,6 +447,7 @@ ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(b_m_ready);
+      if (s + 1 < nsteps) prefix(s + 1);   // nothing of step s needs total, cum_i, dt_i or lb any more
 
       // ---- E3: Y -> storage dtype -> the buffer x occupied (x is dead once Y is complete);
       //      the producer warp stores the tile with one TMA copy ----
