@@ -16,11 +16,16 @@
 //                                            overwritten in place as 16-bit in TMEM        (128x64x128)
 //
 //   warps 0-3   thread i = row i of the step = TMEM lane i: prefix sum of dt*A (each warp scans all
-//               128 values itself, so no cross-warp exchange), the scaled copies of C, x and S, the
-//               decay/mask pass over G, and the epilogue (Y -> 16 bit -> global)
+//               128 values itself, so no cross-warp exchange; done a step ahead, while the last
+//               product of the previous step runs), the scaled copies of x and S, the decay/mask
+//               pass over G (an exponential per element only in the 32-column chunk on the
+//               diagonal; chunks left of it take one factor per row and one per column), and the
+//               epilogue (Y -> 16 bit -> staging buffer)
 //   warp 4      TMA producer: the C, B and x tiles of the next step, each issued as soon as the
 //               product that last read its buffer has retired, and the TMA store of the finished
-//               Y tile (staged by the element-wise warps in the buffer x occupied)
+//               Y tile (staged by the element-wise warps in the buffer x occupied).  The two 16 KB
+//               buffers for x and for the state copy / w*x swap roles every step, so that x(s+1)
+//               is loaded right after the state update of step s instead of after the Y store
 //   warp 5      MMA issuer, operand descriptors built once
 //
 // All exponents are <= 0 (A < 0), so nothing overflows.  TMEM: columns 0-127 hold G, then the masked
@@ -64,6 +69,15 @@ __device__ __forceinline__ void ssd_report(int *status, int code, int detail) {
     status[2] = detail;
     status[3] = static_cast<int>(threadIdx.x);
   }
+}
+
+// A load that stays where it is written: the compiler may neither sink it to its first use nor re-issue it
+// there (it does both with a plain load from a const __restrict__ pointer), which is the point of a prefetch
+// into registers a whole step ahead.
+__device__ __forceinline__ float ldg_pinned(const float *p) {
+  float v;
+  asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(p));
+  return v;
 }
 
 __device__ __forceinline__ float lg2(float x) {
@@ -289,7 +303,8 @@ ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       for (int e = 0; e < 4; ++e) dt4[e] = dt_next[e];
       if (sp + 1 < nsteps) {  // the dt of the step after, fetched a whole step ahead
 #pragma unroll
-        for (int e = 0; e < 4; ++e) dt_next[e] = dt[(static_cast<size_t>(b) * L + static_cast<size_t>(sp + 1) * kQ + 4 * lane + e) * H + h];
+        for (int e = 0; e < 4; ++e)
+          dt_next[e] = ldg_pinned(dt + (static_cast<size_t>(b) * L + static_cast<size_t>(sp + 1) * kQ + 4 * lane + e) * H + h);
       }
       cum4[0] = dt4[0] * a_log2;
 #pragma unroll
