@@ -108,3 +108,15 @@ def test_runtime_rejects_cpu_tensors(native_lib):
         runtime.attn_fwd(t, t, t, t, shape=(1, 1, 128, 128), kv_len=128, dtype="bf16", scale_log2=0.1, causal=False)
     with pytest.raises(TypeError, match="torch.Tensor"):
         runtime.attn_fwd(1, t, t, t, shape=(1, 1, 128, 128), kv_len=128, dtype="bf16", scale_log2=0.1, causal=False)
+
+
+def test_torch_library_ops_are_registered_and_refuse_cpu_tensors(native_lib):
+    import torch
+
+    from neptune_mlir import torch_ops
+
+    for name in torch_ops.OPS:
+        assert hasattr(torch.ops.nb200, name)
+    q = torch.zeros((1, 1, 128, 128), dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="CUDA tensor"):
+        torch.ops.nb200.attn_fwd(q, q, q, torch.empty_like(q), 0.1, True)
