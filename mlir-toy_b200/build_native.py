@@ -25,6 +25,8 @@ CSRC = PKG / "csrc"
 INCLUDE = PKG.parent / "include"
 OBJ_DIR = PKG / "build"
 OUT = PKG / "neptune_mlir" / "_native" / "libnb200.so"
+FRONT_SRC = CSRC / "htile_front" / "htile_front.cpp"
+FRONT_OUT = PKG / "neptune_mlir" / "_native" / "libhtile_front.so"
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -59,9 +61,26 @@ def _compile(src: Path, obj: Path, verbose: bool) -> str:
     return log
 
 
+def build_front(force: bool = False) -> Path:
+    """The HTile front end: host C++ only (g++), a shared library of its own next to the kernel library."""
+    FRONT_OUT.parent.mkdir(parents=True, exist_ok=True)
+    newest = max(FRONT_SRC.stat().st_mtime, (INCLUDE / "htile_front.h").stat().st_mtime)
+    if force or not FRONT_OUT.exists() or FRONT_OUT.stat().st_mtime < newest:
+        gxx = shutil.which("g++") or shutil.which("c++")
+        if gxx is None:
+            raise RuntimeError("g++ not found; the HTile front end cannot be built")
+        cmd = [gxx, "-O2", "-std=c++17", "-Wall", "-Wextra", "-shared", "-fPIC", f"-I{INCLUDE}", "-o", str(FRONT_OUT),
+               str(FRONT_SRC)]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError(f"g++ failed on {FRONT_SRC.name}:\n{res.stdout}\n{res.stderr}")
+    return FRONT_OUT
+
+
 def build(force: bool = False, verbose: bool = False) -> Path:
     OBJ_DIR.mkdir(exist_ok=True)
     OUT.parent.mkdir(parents=True, exist_ok=True)
+    build_front(force)
     sources = sorted(CSRC.glob("*.cu"))
     hdr_time = max(_newest_header(), Path(__file__).stat().st_mtime)
     jobs = []

@@ -4,8 +4,10 @@ Same entry-point shapes as the reference's module of this name
 (src/neptune_mlir/translators/common.py:200-241): ``parse_mlir_module`` turns a ``.mlir`` path into a
 module object after an optional pass pipeline, ``translate_file_with`` feeds it to a translator
 class.  The reference shells out to ``mlir-opt`` and parses with ``mlir.ir``; here the stand-alone
-reader in ``neptune_mlir.htile_text`` and the rewrites in ``neptune_mlir.passes`` do that work, so
-``plugin`` / ``pass_plugin`` (paths to the dialect plugin there) are accepted and unused.
+C++ front end (``neptune_mlir.htile_native`` over libhtile_front.so) does that work, or, where that
+library has not been built, the Python reader in ``neptune_mlir.htile_text`` with the rewrites in
+``neptune_mlir.passes``; ``plugin`` / ``pass_plugin`` (paths to the dialect plugin there) are
+accepted and unused.
 """
 
 from __future__ import annotations
@@ -86,10 +88,32 @@ def parse_mlir_module(path: str, plugin: str | None = None, pass_pipeline: str |
     """
     del plugin, pass_plugin
     try:
+        if front_end() == "native":
+            from .. import htile_native
+
+            return htile_native.parse_file(path, pass_pipeline)
         module = ht.parse_file(path)
         return run_pipeline(module, pass_pipeline)
     except (ht.HTileSyntaxError, PassError) as exc:
         raise RuntimeError(f"HTile front end failed on {path}: {exc}") from exc
+
+
+def front_end() -> str:
+    """Which reader parses and rewrites programs: the C++ front end ("native") or the Python one ("python").
+
+    ``$NEPTUNE_HTILE_FRONT`` chooses; unset, the C++ library is used when it has been built.  Both
+    produce the same object model (checked over the program corpus by the tests).
+    """
+    import os
+
+    choice = os.environ.get("NEPTUNE_HTILE_FRONT", "").strip().lower()
+    if choice in ("native", "python"):
+        return choice
+    if choice:
+        raise ValueError(f"NEPTUNE_HTILE_FRONT must be 'native' or 'python', got {choice!r}")
+    from .. import htile_native
+
+    return "native" if htile_native.available() else "python"
 
 
 def translate_file_with(path: str, translator_cls: Type, plugin: str | None = None,

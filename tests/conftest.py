@@ -18,11 +18,12 @@ def pytest_configure(config):
 
 @pytest.fixture(scope="session")
 def native_lib():
-    """Path of libnb200.so, building it with nvcc if it is not there yet (no GPU needed to build)."""
-    from neptune_mlir.plugin import find_library_path
+    """Path of libnb200.so, building it (nvcc) and the HTile front end (g++) if either is not there yet; no GPU
+    is needed to build."""
+    from neptune_mlir.plugin import find_front_path, find_library_path
 
     path = find_library_path()
-    if path is None:
+    if path is None or find_front_path() is None:
         import importlib.util
 
         spec = importlib.util.spec_from_file_location("nb200_build_native", PKG / "build_native.py")

@@ -3,9 +3,10 @@
 
 The reference's Triton translator (src/neptune_mlir/translators/triton.py in the reference tree) is
 imported UNMODIFIED, under the module name ``ref_neptune_mlir`` and with the ``mlir`` stand-in of
-``tests/golden/mlir_standin`` in place of the LLVM bindings it wants.  HTile text is read by this
-build's reader (``neptune_mlir.htile_text``), rewritten by this build's dot-transpose pass, wrapped
-in the stand-in's object model and handed to ``Translator().translate``.
+``tests/golden/mlir_standin`` in place of the LLVM bindings it wants.  HTile text is read and rewritten
+(dot-transpose pass) by this build's C++ front end (``neptune_mlir.htile_native``) -- and, as a second
+check, by the Python reader and pass -- wrapped in the stand-in's object model and handed to
+``Translator().translate``.
 
 1. Check of the stand-in: the reference's own program (tests/data/flash_attention_htile.mlir) must
    translate to all three of its golden texts (tests/golden/flash_attention_{triton,tilelang,cutile}.py)
@@ -44,7 +45,7 @@ sys.path.insert(0, str(ROOT / "mlir-toy_b200"))
 sys.path.insert(0, str(HERE / "mlir_standin"))
 
 import mlir.ir as standin_ir  # noqa: E402  (the stand-in)
-from neptune_mlir import htile_text, passes, programs  # noqa: E402
+from neptune_mlir import htile_native, htile_text, passes, programs  # noqa: E402
 from oracle.inputs import attention_inputs  # noqa: E402
 
 # name -> (B, H, S, D, dtype, tile_m, tile_n, config index for the input seeds)
@@ -82,24 +83,28 @@ def fold_unit_launch_ids(module) -> None:
                     passes._replace_all_uses(module, body.arguments[i], zero)
 
 
-def translate(ref_translator, text: str, run_pass: bool = True) -> str:
-    module = htile_text.parse_module(text)
-    if run_pass:
-        passes.dot_transpose_to_load_order(module)
+def translate(ref_translator, text: str, run_pass: bool = True, front: str = "native") -> str:
+    if front == "native":   # the C++ front end reads, verifies and rewrites
+        module = htile_native.parse_module(text, passes.PASS_PIPELINE if run_pass else None)
+    else:                   # the Python reader and pass
+        module = htile_text.parse_module(text)
+        if run_pass:
+            passes.dot_transpose_to_load_order(module)
     fold_unit_launch_ids(module)
     return ast.unparse(ref_translator.Translator().translate(standin_ir.from_htile(module)))
 
 
 def check_standin(ref, ref_root: Path) -> None:
     text = (ref_root / "tests" / "data" / "flash_attention_htile.mlir").read_text()
-    for name, mod in ref.items():
-        got = translate(mod, text, run_pass=(name != "tilelang"))
-        want = (ref_root / "tests" / "golden" / f"flash_attention_{name}.py").read_text()
-        if got.strip() != want.strip():
-            import difflib
-            sys.stdout.writelines(difflib.unified_diff(want.splitlines(True), got.splitlines(True), "golden", "stand-in"))
-            raise SystemExit(f"the stand-in does not reproduce the reference's golden {name} translation")
-        print(f"stand-in reproduces tests/golden/flash_attention_{name}.py byte for byte")
+    for front in ("native", "python"):
+        for name, mod in ref.items():
+            got = translate(mod, text, run_pass=(name != "tilelang"), front=front)
+            want = (ref_root / "tests" / "golden" / f"flash_attention_{name}.py").read_text()
+            if got.strip() != want.strip():
+                import difflib
+                sys.stdout.writelines(difflib.unified_diff(want.splitlines(True), got.splitlines(True), "golden", "stand-in"))
+                raise SystemExit(f"{front} front end + stand-in do not reproduce the reference's golden {name} translation")
+            print(f"{front} front end + stand-in reproduce tests/golden/flash_attention_{name}.py byte for byte")
 
 
 def sha_tensors(*tensors) -> str:
