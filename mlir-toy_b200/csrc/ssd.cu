@@ -50,14 +50,15 @@ constexpr int kBCBytes = kQ * kN * 2;      // 32 KB: two 64-column boxes of 16 K
 constexpr int kBCBox = kBCBytes / 2;
 constexpr int kXBytes = kQ * kP * 2;       // 16 KB: one box
 constexpr int kTileBytes = 2 * kBCBytes + kXBytes;
-constexpr int kSsdSmem = 2 * kBCBytes + 2 * kXBytes + 4 * 2 * kQ * 4 /*lb, cf*/ + 256 /*barriers*/;
+constexpr int kDtBytes = kQ * 4 * 4;      // 128 rows x 4 heads of dt (fp32): the 16-byte minimum of a TMA box row
+constexpr int kSsdSmem = 2 * kBCBytes + 2 * kXBytes + 4 * 2 * kQ * 4 /*lb, cf*/ + 2 * kDtBytes + 256 /*barriers*/;
 constexpr int kSsdTmemCols = 256;
 constexpr float kLog2e = 1.4426950408889634f;
 
 enum : int { kErrSsdProducer = 11, kErrSsdMma = 12, kErrSsdCompute = 13, kErrSsdAlign = 15 };
 
 struct SsdBarriers {
-  uint64_t c_full, b_full, x_full, z_done, y_staged, y_free, e1a, inter_done, e1b, g_ready, m_ready, y_ready;
+  uint64_t c_full, b_full, x_full, z_done, y_staged, y_free, e1a, inter_done, e1b, g_ready, m_ready, y_ready, dt_full[2];
   uint32_t tmem_base;
   int abort_flag;
   int skip;
@@ -92,7 +93,8 @@ __device__ __forceinline__ uint32_t sw128(int r, int c) { return r * 128 + ((c ^
 template <int DT>
 __global__ void __launch_bounds__(kSsdThreads, 2)
 ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_b,
-                 const __grid_constant__ CUtensorMap tm_c, const __grid_constant__ CUtensorMap tm_y, const float *__restrict__ dt, const float *__restrict__ A,
+                 const __grid_constant__ CUtensorMap tm_c, const __grid_constant__ CUtensorMap tm_y,
+                 const __grid_constant__ CUtensorMap tm_dt, int dt_by_tma, const float *__restrict__ dt, const float *__restrict__ A,
                  uint16_t *__restrict__ y, int L, int H, int G, int *status) {
   extern __shared__ __align__(1024) unsigned char smem[];
   const uint32_t base = smem_u32(smem);
@@ -105,7 +107,9 @@ ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
   const uint32_t sB = base, sC = base + kBCBytes, sU = base + 2 * kBCBytes;
   unsigned char *pU = smem + 2 * kBCBytes;
   float *lb_all = reinterpret_cast<float *>(smem + 2 * kBCBytes + 2 * kXBytes);  // [4 warps][lb 128 | cf 128]
-  SsdBarriers *bars = reinterpret_cast<SsdBarriers *>(smem + 2 * kBCBytes + 2 * kXBytes + 4 * 2 * kQ * 4);
+  const float *dt_tile = reinterpret_cast<const float *>(smem + 2 * kBCBytes + 2 * kXBytes + 4 * 2 * kQ * 4);  // [2][128][4]
+  const uint32_t sDt = base + 2 * kBCBytes + 2 * kXBytes + 4 * 2 * kQ * 4;
+  SsdBarriers *bars = reinterpret_cast<SsdBarriers *>(smem + 2 * kBCBytes + 2 * kXBytes + 4 * 2 * kQ * 4 + 2 * kDtBytes);
   volatile int *abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -128,6 +132,8 @@ ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
     mbar_init(smem_u32(&bars->g_ready), 1);
     mbar_init(smem_u32(&bars->m_ready), 128);
     mbar_init(smem_u32(&bars->y_ready), 1);
+    mbar_init(smem_u32(&bars->dt_full[0]), 1);
+    mbar_init(smem_u32(&bars->dt_full[1]), 1);
     fence_barrier_init();
     fence_proxy_async_smem();
   }
@@ -143,6 +149,7 @@ ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
     tma_prefetch_desc(&tm_b);
     tma_prefetch_desc(&tm_c);
     tma_prefetch_desc(&tm_y);
+    if (dt_by_tma) tma_prefetch_desc(&tm_dt);
   }
   tc_fence_before();
   __syncthreads();
@@ -154,13 +161,14 @@ ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
                  b_x_full = smem_u32(&bars->x_full), b_z_done = smem_u32(&bars->z_done),
                  b_y_staged = smem_u32(&bars->y_staged), b_y_free = smem_u32(&bars->y_free), b_e1a = smem_u32(&bars->e1a), b_inter_done = smem_u32(&bars->inter_done),
                  b_e1b = smem_u32(&bars->e1b), b_g_ready = smem_u32(&bars->g_ready),
-                 b_m_ready = smem_u32(&bars->m_ready), b_y_ready = smem_u32(&bars->y_ready);
+                 b_m_ready = smem_u32(&bars->m_ready), b_y_ready = smem_u32(&bars->y_ready),
+                 b_dt_full = smem_u32(&bars->dt_full[0]);  // buffer p is at + 8 * p
 
   if (warp == 4) {
     // ================================ TMA producer ================================
     if (lane == 0) {
       bool ok = true;
-      int issued_c = 0, issued_b = 0, issued_x = 0;
+      int issued_c = 0, issued_b = 0, issued_x = 0, issued_dt = 0;
       auto load_c = [&](int s) {
         const int row = b * L + s * kQ;
         mbar_arrive_expect_tx(b_c_full, kBCBytes);
@@ -180,6 +188,16 @@ ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
         tma_load_2d(sU + (s & 1) * kXBytes, &tm_x, h * kP, b * L + s * kQ, b_x_full);
         ++issued_x;
       };
+      // dt of one step for the four heads around h (a TMA box row cannot be narrower than 16 bytes): a strided
+      // gather that the copy engine does well and 128 threads doing 4-byte loads 256 bytes apart do badly
+      auto load_dt = [&](int s) {
+        if (!dt_by_tma) return;
+        mbar_arrive_expect_tx(b_dt_full + 8 * (s & 1), kDtBytes);
+        tma_load_2d(sDt + (s & 1) * kDtBytes, &tm_dt, h & ~3, b * L + s * kQ, b_dt_full + 8 * (s & 1));
+        ++issued_dt;
+      };
+      load_dt(0);
+      if (nsteps > 1) load_dt(1);
       load_c(0);
       load_b(0);
       load_x(0);
@@ -192,6 +210,7 @@ ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
           ok = mbar_wait(b_inter_done, ph, abort_flag);
           if (!ok) { ssd_report(status, kErrSsdProducer, 4 * s); break; }
           load_c(s + 1);
+          if (s + 2 < nsteps) load_dt(s + 2);   // its buffer held dt(s), consumed before this step's first product
           ok = mbar_wait(b_z_done, ph, abort_flag);
           if (!ok) { ssd_report(status, kErrSsdProducer, 4 * s + 1); break; }
           load_b(s + 1);
@@ -214,7 +233,12 @@ ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
           const bool c_ok = issued_c == 0 || mbar_try_wait(b_c_full, (issued_c - 1) & 1);
           const bool b_ok = issued_b == 0 || mbar_try_wait(b_b_full, (issued_b - 1) & 1);
           const bool x_ok = issued_x == 0 || mbar_try_wait(b_x_full, (issued_x - 1) & 1);
-          if (c_ok && b_ok && x_ok) break;
+          bool d_ok = true;
+          for (int n = 0; n < 2; ++n) {  // the last two dt loads
+            const int sd = issued_dt - 1 - n;
+            if (sd >= 0) d_ok = d_ok && mbar_try_wait(b_dt_full + 8 * (sd & 1), (sd >> 1) & 1);
+          }
+          if (c_ok && b_ok && x_ok && d_ok) break;
           __nanosleep(100);
         }
       }
@@ -291,17 +315,24 @@ ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
     bool ok = true;
     float dt_next[4];
 #pragma unroll
-    for (int e = 0; e < 4; ++e) dt_next[e] = dt[(static_cast<size_t>(b) * L + 4 * lane + e) * H + h];
+    for (int e = 0; e < 4; ++e) dt_next[e] = dt_by_tma ? 0.f : dt[(static_cast<size_t>(b) * L + 4 * lane + e) * H + h];
     // Prefix sum of dt*A over the 128 rows of step sp, every warp for itself (lane l holds rows 4l..4l+3);
     // leaves total, cum_i and dt_i of this thread's row and this warp's copy of cum_j - log2(dt_j) in lb.
     // Depends only on dt, so it runs for step s+1 while the last product of step s is in flight.
     float total = 0.f, cum_i = 0.f, dt_i = 0.f;
     float ref0 = 0.f, ref1 = 0.f, ref2 = 0.f;   // cum at the last row of column chunks 0..2 (32 columns each)
-    auto prefix = [&](int sp) {
+    auto prefix = [&](int sp) -> bool {
       float dt4[4], cum4[4];
+      if (dt_by_tma) {
+        if (!__all_sync(0xffffffffu, mbar_wait(b_dt_full + 8 * (sp & 1), (sp >> 1) & 1, abort_flag))) return false;
+        const float *tile = dt_tile + (sp & 1) * (kQ * 4) + (h & 3);
 #pragma unroll
-      for (int e = 0; e < 4; ++e) dt4[e] = dt_next[e];
-      if (sp + 1 < nsteps) {  // the dt of the step after, fetched a whole step ahead
+        for (int e = 0; e < 4; ++e) dt4[e] = tile[(4 * lane + e) * 4];
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) dt4[e] = dt_next[e];
+      }
+      if (!dt_by_tma && sp + 1 < nsteps) {  // the dt of the step after, fetched a whole step ahead
 #pragma unroll
         for (int e = 0; e < 4; ++e)
           dt_next[e] = ldg_pinned(dt + (static_cast<size_t>(b) * L + static_cast<size_t>(sp + 1) * kQ + 4 * lane + e) * H + h);
@@ -343,10 +374,13 @@ ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
         const float cv = __shfl_sync(0xffffffffu, cum4[e], src), dv = __shfl_sync(0xffffffffu, dt4[e], src);
         if (comp == e) { cum_i = cv; dt_i = dv; }
       }
-
+      return true;
     };
-    prefix(0);
-    for (int s = 0; s < nsteps; ++s) {
+    if (!prefix(0)) {
+      ssd_report(status, kErrSsdCompute, -1);
+      ok = false;
+    }
+    for (int s = 0; s < nsteps && ok; ++s) {
       const uint32_t ph = s & 1;
       unsigned char *pX = pU + (s & 1) * kXBytes, *pXs = pU + ((s & 1) ^ 1) * kXBytes;
 
@@ -462,7 +496,11 @@ ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(b_m_ready);
-      if (s + 1 < nsteps) prefix(s + 1);   // nothing of step s needs total, cum_i, dt_i or lb any more
+      if (s + 1 < nsteps && !prefix(s + 1)) {  // nothing of step s needs total, cum_i, dt_i or lb any more
+        ssd_report(status, kErrSsdCompute, 8 * s + 6);
+        ok = false;
+        break;
+      }
 
       // ---- E3: Y -> storage dtype -> the buffer x occupied (x is dead once Y is complete);
       //      the producer warp stores the tile with one TMA copy ----
@@ -502,16 +540,23 @@ ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
 template <int DT>
 int launch_ssd(const void *x, const float *dt, const float *A, const void *Bm, const void *Cm, void *y, int B, int L,
                int H, int G, int dtype, int *status, cudaStream_t st) {
-  CUtensorMap tx, tb, tc, ty;
+  CUtensorMap tx, tb, tc, ty, tdt;
   int rc;
   if ((rc = tma_map_2d_sw128(&tx, x, (long long)B * L, (long long)H * kP, dtype, kQ, "ssd_chunk_scan")) != NB200_OK) return rc;
   if ((rc = tma_map_2d_sw128(&tb, Bm, (long long)B * L, (long long)G * kN, dtype, kQ, "ssd_chunk_scan")) != NB200_OK) return rc;
   if ((rc = tma_map_2d_sw128(&tc, Cm, (long long)B * L, (long long)G * kN, dtype, kQ, "ssd_chunk_scan")) != NB200_OK) return rc;
   if ((rc = tma_map_2d_sw128(&ty, y, (long long)B * L, (long long)H * kP, dtype, kQ, "ssd_chunk_scan")) != NB200_OK) return rc;
+  // dt through the copy engine needs rows of H floats to be a multiple of 16 bytes and a 16-byte aligned base
+  const int dt_by_tma = (H % 4 == 0 && aligned16(dt)) ? 1 : 0;
+  if (dt_by_tma) {
+    if ((rc = tma_map_2d_f32(&tdt, dt, (long long)B * L, H, 4, kQ, "ssd_chunk_scan")) != NB200_OK) return rc;
+  } else {
+    tdt = tx;  // never used by the kernel
+  }
   NB200_CHECK_CUDA(cudaFuncSetAttribute(ssd_fused_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSsdSmem));
   NB200_CHECK_CUDA(cudaFuncSetAttribute(ssd_fused_kernel<DT>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                         cudaSharedmemCarveoutMaxShared));
-  ssd_fused_kernel<DT><<<dim3(B * H), dim3(kSsdThreads), kSsdSmem, st>>>(tx, tb, tc, ty, dt, A, static_cast<uint16_t *>(y),
+  ssd_fused_kernel<DT><<<dim3(B * H), dim3(kSsdThreads), kSsdSmem, st>>>(tx, tb, tc, ty, tdt, dt_by_tma, dt, A, static_cast<uint16_t *>(y),
                                                                          L, H, G, status);
   NB200_CHECK_CUDA(cudaGetLastError());
   return NB200_OK;

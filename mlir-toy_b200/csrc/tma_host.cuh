@@ -42,4 +42,20 @@ inline int tma_map_2d_sw128(CUtensorMap *tm, const void *ptr, long long rows, lo
   return NB200_OK;
 }
 
+// Row-major [rows, cols] fp32 tensor; boxes of box_rows x box_cols (box_cols * 4 bytes a multiple of 16), no swizzle.
+inline int tma_map_2d_f32(CUtensorMap *tm, const void *ptr, long long rows, long long cols, int box_cols, int box_rows,
+                          const char *who) {
+  EncodeTiledFnT enc = tma_encode_fn();
+  NB200_REQUIRE(enc, NB200_ERR_LAUNCH, "%s: cuTensorMapEncodeTiled is not available from the driver", who);
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 4};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void *>(ptr), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  NB200_REQUIRE(r == CUDA_SUCCESS, NB200_ERR_LAUNCH, "%s: cuTensorMapEncodeTiled failed with code %d", who, (int)r);
+  return NB200_OK;
+}
+
 }  // namespace nb200

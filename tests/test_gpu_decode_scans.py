@@ -174,6 +174,23 @@ def test_ssd_small(cuda, native_lib, chunk, G):
     assert_rms_close(y, faithful, 2.0 ** -8)
 
 
+def test_ssd_head_count_not_a_multiple_of_four(cuda, native_lib):
+    """With H % 4 != 0 a row of dt is not a multiple of 16 bytes: the kernel reads dt with plain loads instead of TMA."""
+    from neptune_mlir import runtime
+
+    B, L, H, P, N, G, chunk = 1, 384, 3, 64, 128, 1, 128
+    x, dt, A, Bm, Cm = inputs.ssd_inputs(B=B, L=L, H=H, P=P, N=N, G=G)
+    ws = torch.empty(runtime.ssd_workspace_bytes(B, L, H, P, N, G, chunk), dtype=torch.uint8, device=cuda)
+    y = torch.full((B, L, H, P), float("nan"), dtype=torch.bfloat16, device=cuda)
+    runtime.ssd_chunk_scan(x.to(cuda), dt.to(cuda), A.to(cuda), Bm.to(cuda), Cm.to(cuda), ws, y, B=B, L=L, H=H, P=P,
+                           N=N, G=G, chunk=chunk, dtype="bf16")
+    finish()
+    runtime.check_workspace_status(ws)
+    ref = ssd.ssd_reference(x, dt, A, Bm, Cm)
+    assert_storage_close(y, ref, BF16_ATOL, 2 * BF16_ULP, scale_by_rms=True)
+    assert_rms_close(y, ref, 2.0 ** -8)
+
+
 def test_ssd_config5_full_size_sampled(cuda, native_lib):
     """B=4, L=8192, H=64, P=64, N=128, chunk 256; heads are independent, a sample is checked in full."""
     from neptune_mlir import runtime
