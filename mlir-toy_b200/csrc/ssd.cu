@@ -387,29 +387,30 @@ ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       // ---- E1a: S_in -> 16 bit in smem; S *= e^cum_last.  (The state is final: the previous step's
       //      y_ready, waited for in E3, was committed after its state update.) ----
       {
-        if (s > 0) {  // the copy goes where Y(s-1) was staged: its store must have read the buffer
-          ok = __all_sync(0xffffffffu, mbar_wait(b_y_free, (s - 1) & 1, abort_flag));
-          if (!ok) { ssd_report(status, kErrSsdCompute, 8 * s + 5); break; }
-        }
         uint32_t sv[kP];
         tmem_ld32p(tS + lane_addr, sv);
         tmem_ld32p(tS + lane_addr + 32, sv + 32);
         tmem_wait_ld();
         const float et = ex2(total);
+        uint4 cp[8];  // the 16-bit copy, held back until its buffer is free
 #pragma unroll
         for (int cc = 0; cc < 8; ++cc) {
-          uint4 w;
-          w.x = pack2<DT>(__uint_as_float(sv[8 * cc + 0]), __uint_as_float(sv[8 * cc + 1]));
-          w.y = pack2<DT>(__uint_as_float(sv[8 * cc + 2]), __uint_as_float(sv[8 * cc + 3]));
-          w.z = pack2<DT>(__uint_as_float(sv[8 * cc + 4]), __uint_as_float(sv[8 * cc + 5]));
-          w.w = pack2<DT>(__uint_as_float(sv[8 * cc + 6]), __uint_as_float(sv[8 * cc + 7]));
-          *reinterpret_cast<uint4 *>(pXs + sw128(i, cc)) = w;
+          cp[cc].x = pack2<DT>(__uint_as_float(sv[8 * cc + 0]), __uint_as_float(sv[8 * cc + 1]));
+          cp[cc].y = pack2<DT>(__uint_as_float(sv[8 * cc + 2]), __uint_as_float(sv[8 * cc + 3]));
+          cp[cc].z = pack2<DT>(__uint_as_float(sv[8 * cc + 4]), __uint_as_float(sv[8 * cc + 5]));
+          cp[cc].w = pack2<DT>(__uint_as_float(sv[8 * cc + 6]), __uint_as_float(sv[8 * cc + 7]));
         }
 #pragma unroll
         for (int k = 0; k < kP; ++k) sv[k] = __float_as_uint(__uint_as_float(sv[k]) * et);
         tmem_st32(tS + lane_addr, *reinterpret_cast<uint32_t(*)[32]>(sv));
         tmem_st32(tS + lane_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(sv + 32));
+        if (s > 0) {  // the copy goes where Y(s-1) was staged: its store must have read the buffer
+          ok = __all_sync(0xffffffffu, mbar_wait(b_y_free, (s - 1) & 1, abort_flag));
+        }
+#pragma unroll
+        for (int cc = 0; cc < 8; ++cc) *reinterpret_cast<uint4 *>(pXs + sw128(i, cc)) = cp[cc];
         tmem_wait_st();
+        if (!ok) { ssd_report(status, kErrSsdCompute, 8 * s + 5); break; }
         tc_fence_before();
         fence_proxy_async_smem();   // the tensor core reads shared memory through the async proxy
         mbar_arrive(b_e1a);
