@@ -57,7 +57,7 @@ template <int N> __device__ __forceinline__ void cp_async_wait() {
 }
 
 template <int DT>
-__global__ void __launch_bounds__(kScanThreads, 10)
+__global__ void __launch_bounds__(kScanThreads, 7)
 selective_scan_kernel(const uint16_t *__restrict__ u, const uint16_t *__restrict__ delta,
                       const float *__restrict__ A, const uint16_t *__restrict__ Bm,
                       const uint16_t *__restrict__ Cm, const float *__restrict__ Dskip,
