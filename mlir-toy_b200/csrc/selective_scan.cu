@@ -24,8 +24,6 @@
 namespace nb200 {
 namespace {
 
-constexpr int kScanThreads = 64;
-constexpr int kNPT = 8;                       // states per thread (two threads per channel)
 constexpr int kDB = 32;                       // channels per CTA
 constexpr int kLC = 32;                       // time steps per staged chunk
 constexpr int kRowBytes = kLC * 2 + 16;       // padded row of a 16-bit tile
@@ -56,26 +54,41 @@ template <int N> __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
-template <int DT>
-__global__ void __launch_bounds__(kScanThreads, 7)
+// NPT = states per thread (8, 4 or 2), so 16 / NPT threads share a channel and a CTA of 32 channels has
+// 512 / NPT threads.  8 states per thread is the cheapest per update (the per-step scalar work is spread over
+// more states) and is used when the problem fills the GPU; smaller problems take 4 or 2, which multiplies the
+// number of warps: a lone warp per scheduler is held by its own exp2 issue rate (one warp instruction per
+// 8 cycles), so the time of a small problem is set by the states per thread, not by the work.
+template <int NPT> constexpr int scan_min_ctas() { return NPT == 8 ? 7 : (NPT == 4 ? 4 : 2); }
+
+template <int DT, int NPT>
+__global__ void __launch_bounds__(512 / NPT, scan_min_ctas<NPT>())
 selective_scan_kernel(const uint16_t *__restrict__ u, const uint16_t *__restrict__ delta,
                       const float *__restrict__ A, const uint16_t *__restrict__ Bm,
                       const uint16_t *__restrict__ Cm, const float *__restrict__ Dskip,
                       const uint16_t *__restrict__ z, uint16_t *__restrict__ out, int Dm, int L) {
+  constexpr int TPC = kStates / NPT;          // threads per channel: 2, 4 or 8
+  constexpr int T = kDB * TPC;                // threads per CTA
+  constexpr int NP = NPT / 2;                 // packed pairs of states per thread
+  constexpr int TS = 8 / TPC;                 // time steps of an 8-step group that a lane finishes: 4, 2 or 1
   __shared__ ScanSmem sm;
   const int tid = threadIdx.x;
   const int b = blockIdx.y;
   const int d0 = blockIdx.x * kDB;
-  const int dl = tid >> 1, ng = tid & 1;
+  const int dl = tid / TPC, ng = tid % TPC;
   const int d = d0 + dl;
 
-  // decay rates of this thread's 4 states, in the exp2 domain, as two packed pairs
-  const float4 a4 = *reinterpret_cast<const float4 *>(A + (size_t)d * kStates + ng * kNPT);
-  const float4 a5 = *reinterpret_cast<const float4 *>(A + (size_t)d * kStates + ng * kNPT + 4);
-  const uint64_t A2[4] = {f2_pack(a4.x * kLog2e, a4.y * kLog2e), f2_pack(a4.z * kLog2e, a4.w * kLog2e),
-                          f2_pack(a5.x * kLog2e, a5.y * kLog2e), f2_pack(a5.z * kLog2e, a5.w * kLog2e)};
+  // decay rates of this thread's states, in the exp2 domain, as packed pairs
+  uint64_t A2[NP];
+#pragma unroll
+  for (int i = 0; i < NP; ++i) {
+    const float2 a = *reinterpret_cast<const float2 *>(A + (size_t)d * kStates + ng * NPT + 2 * i);
+    A2[i] = f2_pack(a.x * kLog2e, a.y * kLog2e);
+  }
   const float dskip = Dskip[d];
-  uint64_t h2[4] = {0ull, 0ull, 0ull, 0ull};
+  uint64_t h2[NP];
+#pragma unroll
+  for (int i = 0; i < NP; ++i) h2[i] = 0ull;
 
   const size_t row_base = ((size_t)b * Dm + d0) * L;        // element offset of row d0 of this sequence
   const size_t bc_base = (size_t)b * kStates * L;
@@ -84,16 +97,15 @@ selective_scan_kernel(const uint16_t *__restrict__ u, const uint16_t *__restrict
   auto issue_loads = [&](int chunk, int buf) {
     ScanStage &s = sm.stage[buf];
     const int t0 = chunk * kLC;
-#pragma unroll
-    for (int k = 0; k < 2; ++k) {  // u / delta / z : 32 rows x 4 segments of 16 bytes -> two per thread per tensor
-      const int idx = tid + k * kScanThreads, row = idx >> 2, seg = idx & 3;
+    for (int idx = tid; idx < kDB * 4; idx += T) {  // u / delta / z : 32 rows x 4 segments of 16 bytes
+      const int row = idx >> 2, seg = idx & 3;
       const size_t g = row_base + (size_t)row * L + t0 + seg * 8;
       cp_async16(s.u + row * kRowBytes + seg * 16, u + g);
       cp_async16(s.dl + row * kRowBytes + seg * 16, delta + g);
       cp_async16(s.z + row * kRowBytes + seg * 16, z + g);
     }
-    {  // Bm and Cm: 16 rows x 4 segments each -> one of each per thread
-      const int row = tid >> 2, seg = tid & 3;
+    for (int idx = tid; idx < kStates * 4; idx += T) {  // Bm and Cm: 16 rows x 4 segments each
+      const int row = idx >> 2, seg = idx & 3;
       const size_t g = bc_base + (size_t)row * L + t0 + seg * 8;
       cp_async16(s.braw + row * (kLC * 2) + seg * 16, Bm + g);
       cp_async16(s.craw + row * (kLC * 2) + seg * 16, Cm + g);
@@ -113,8 +125,8 @@ selective_scan_kernel(const uint16_t *__restrict__ u, const uint16_t *__restrict
     __syncthreads();
     ScanStage &s = sm.stage[buf];
 
-    {  // Bm/Cm of this chunk -> fp32 [t][n]; thread = (n, group of 8 time steps)
-      const int n = tid >> 2, tq = tid & 3;
+    for (int idx = tid; idx < kStates * 4; idx += T) {  // Bm/Cm of this chunk -> fp32 [t][n]; item = (n, group of 8 time steps)
+      const int n = idx >> 2, tq = idx & 3;
       const uint4 bw = *reinterpret_cast<const uint4 *>(s.braw + n * (kLC * 2) + tq * 16);
       const uint4 cw = *reinterpret_cast<const uint4 *>(s.craw + n * (kLC * 2) + tq * 16);
       const uint32_t bs[4] = {bw.x, bw.y, bw.z, bw.w}, cs[4] = {cw.x, cw.y, cw.z, cw.w};
@@ -147,14 +159,24 @@ selective_scan_kernel(const uint16_t *__restrict__ u, const uint16_t *__restrict
           const uint64_t dt2 = f2_pack(dd[e], dd[e]);
           const float dtu = dd[e] * uu[e];
           const uint64_t dtu2 = f2_pack(dtu, dtu);
-          const ulonglong2 bv = *reinterpret_cast<const ulonglong2 *>(&sm.bf[t][ng * kNPT]);
-          const ulonglong2 bw = *reinterpret_cast<const ulonglong2 *>(&sm.bf[t][ng * kNPT + 4]);
-          const ulonglong2 cv = *reinterpret_cast<const ulonglong2 *>(&sm.cf[t][ng * kNPT]);
-          const ulonglong2 cw = *reinterpret_cast<const ulonglong2 *>(&sm.cf[t][ng * kNPT + 4]);
-          const uint64_t b2[4] = {bv.x, bv.y, bw.x, bw.y}, c2[4] = {cv.x, cv.y, cw.x, cw.y};
+          uint64_t b2[NP], c2[NP];
+          if constexpr (NPT >= 4) {
+#pragma unroll
+            for (int q = 0; q < NPT / 4; ++q) {
+              const ulonglong2 bv = *reinterpret_cast<const ulonglong2 *>(&sm.bf[t][ng * NPT + 4 * q]);
+              const ulonglong2 cv = *reinterpret_cast<const ulonglong2 *>(&sm.cf[t][ng * NPT + 4 * q]);
+              b2[2 * q] = bv.x;
+              b2[2 * q + 1] = bv.y;
+              c2[2 * q] = cv.x;
+              c2[2 * q + 1] = cv.y;
+            }
+          } else {
+            b2[0] = *reinterpret_cast<const uint64_t *>(&sm.bf[t][ng * NPT]);
+            c2[0] = *reinterpret_cast<const uint64_t *>(&sm.cf[t][ng * NPT]);
+          }
           uint64_t y2 = 0ull;
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
+          for (int i = 0; i < NP; ++i) {
             const float2 x = f2_unpack(f2_mul(dt2, A2[i]));
             const uint64_t a2 = f2_pack(ex2(x.x), ex2(x.y));
             h2[i] = f2_fma(a2, h2[i], f2_mul(dtu2, b2[i]));
@@ -164,39 +186,78 @@ selective_scan_kernel(const uint16_t *__restrict__ u, const uint16_t *__restrict
           y8[tp * 2 + e] = yy.x + yy.y;
         }
       }
-      // The two lanes of a channel exchange halves: lane ng ends with t = 4*ng .. 4*ng+3.
-      float r4[4];
+      // Sum over the lanes of a channel by recursive halving: at distance dist a lane keeps the half of its
+      // time steps that its bit selects and receives the partner's sums for them, so that lane ng ends with
+      // the complete sums of time steps ng*TS .. ng*TS + TS - 1 of the group.
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float keep = ng ? y8[4 + i] : y8[i];
-        const float send = ng ? y8[i] : y8[4 + i];
-        r4[i] = keep + __shfl_xor_sync(0xffffffffu, send, 1);
+      for (int dist = TPC / 2, n = 8; dist >= 1; dist >>= 1, n >>= 1) {
+        const bool upper = (ng & dist) != 0;
+#pragma unroll
+        for (int i = 0; i < n / 2; ++i) {
+          const float keep = upper ? y8[n / 2 + i] : y8[i];
+          const float send = upper ? y8[i] : y8[n / 2 + i];
+          y8[i] = keep + __shfl_xor_sync(0xffffffffu, send, dist);
+        }
       }
-      // skip term and SiLU gate for this lane's four time steps
-      const int off = dl * kRowBytes + t8 * 16 + ng * 8;
-      const uint2 uw2 = *reinterpret_cast<const uint2 *>(s.u + off);
-      const uint2 zw2 = *reinterpret_cast<const uint2 *>(s.z + off);
-      const float2 ua = unpack2<DT>(uw2.x), ub = unpack2<DT>(uw2.y), za = unpack2<DT>(zw2.x), zb = unpack2<DT>(zw2.y);
-      const float uu4[4] = {ua.x, ua.y, ub.x, ub.y}, zz4[4] = {za.x, za.y, zb.x, zb.y};
-      float o4[4];
+      // skip term and SiLU gate for this lane's TS time steps
+      const int off = dl * kRowBytes + t8 * 16 + ng * (TS * 2);
+      float uu4[TS], zz4[TS], o4[TS];
+      if constexpr (TS == 4) {
+        const uint2 uw2 = *reinterpret_cast<const uint2 *>(s.u + off);
+        const uint2 zw2 = *reinterpret_cast<const uint2 *>(s.z + off);
+        const float2 ua = unpack2<DT>(uw2.x), ub = unpack2<DT>(uw2.y), za = unpack2<DT>(zw2.x), zb = unpack2<DT>(zw2.y);
+        uu4[0] = ua.x; uu4[1] = ua.y; uu4[2] = ub.x; uu4[3] = ub.y;
+        zz4[0] = za.x; zz4[1] = za.y; zz4[2] = zb.x; zz4[3] = zb.y;
+      } else if constexpr (TS == 2) {
+        const float2 ua = unpack2<DT>(*reinterpret_cast<const uint32_t *>(s.u + off));
+        const float2 za = unpack2<DT>(*reinterpret_cast<const uint32_t *>(s.z + off));
+        uu4[0] = ua.x; uu4[1] = ua.y;
+        zz4[0] = za.x; zz4[1] = za.y;
+      } else {
+        uu4[0] = load1<DT>(s.u + off, 0);
+        zz4[0] = load1<DT>(s.z + off, 0);
+      }
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float yv = fmaf(dskip, uu4[i], r4[i]);
+      for (int i = 0; i < TS; ++i) {
+        const float yv = fmaf(dskip, uu4[i], y8[i]);
         o4[i] = yv * zz4[i] * __frcp_rn(1.f + ex2(-zz4[i] * kLog2e));
       }
-      *reinterpret_cast<uint2 *>(sm.out + off) = make_uint2(pack2<DT>(o4[0], o4[1]), pack2<DT>(o4[2], o4[3]));
+      if constexpr (TS == 4) {
+        *reinterpret_cast<uint2 *>(sm.out + off) = make_uint2(pack2<DT>(o4[0], o4[1]), pack2<DT>(o4[2], o4[3]));
+      } else if constexpr (TS == 2) {
+        *reinterpret_cast<uint32_t *>(sm.out + off) = pack2<DT>(o4[0], o4[1]);
+      } else {
+        store1<DT>(sm.out + off, 0, o4[0]);
+      }
     }
     __syncthreads();
 
-#pragma unroll
-    for (int k = 0; k < 2; ++k) {  // output tile -> global, two 16-byte segments per thread (rows are 64 contiguous bytes)
-      const int idx = tid + k * kScanThreads, row = idx >> 2, seg = idx & 3;
+    for (int idx = tid; idx < kDB * 4; idx += T) {  // output tile -> global in 16-byte segments (rows are 64 contiguous bytes)
+      const int row = idx >> 2, seg = idx & 3;
       const uint4 w = *reinterpret_cast<const uint4 *>(sm.out + row * kRowBytes + seg * 16);
       *reinterpret_cast<uint4 *>(out + row_base + (size_t)row * L + chunk * kLC + seg * 8) = w;
     }
     // The next iteration's first barrier orders these reads of sm.out before its next writes, and
     // its cp.async into stage[buf] is issued after the barrier above, i.e. after every read of it.
   }
+}
+
+template <int DT, int NPT>
+void launch_scan(const void *u, const void *delta, const float *A, const void *Bm, const void *Cm, const float *Dskip,
+                 const void *z, void *out, int B, int Dm, int L, cudaStream_t st) {
+  const dim3 grid(Dm / kDB, B), block(512 / NPT);
+  selective_scan_kernel<DT, NPT><<<grid, block, 0, st>>>(
+      static_cast<const uint16_t *>(u), static_cast<const uint16_t *>(delta), A, static_cast<const uint16_t *>(Bm),
+      static_cast<const uint16_t *>(Cm), Dskip, static_cast<const uint16_t *>(z), static_cast<uint16_t *>(out), Dm, L);
+}
+
+// States per thread for a problem of `ctas` CTAs on a GPU of `sms` SMs: the largest of 8, 4, 2 that still gives
+// every warp scheduler (four per SM) about three warps.
+int states_per_thread(long long ctas, int sms) {
+  const long long want = 3ll * 4 * sms;
+  if (ctas * 2 >= want) return 8;
+  if (ctas * 4 >= want) return 4;
+  return 2;
 }
 
 }  // namespace
@@ -218,15 +279,20 @@ extern "C" int nb200_selective_scan_fwd(const void *u, const void *delta, const 
                 "selective_scan: L must be a multiple of 64 and D_inner a multiple of %d", kDB);
   NB200_REQUIRE(B <= 65535, NB200_ERR_UNSUPPORTED, "selective_scan: batch too large");
   auto st = static_cast<cudaStream_t>(stream);
-  const dim3 grid(Dm / kDB, B), block(kScanThreads);
-#define NB200_SCAN_ARGS                                                                              \
-  static_cast<const uint16_t *>(u), static_cast<const uint16_t *>(delta), A,                         \
-      static_cast<const uint16_t *>(Bm), static_cast<const uint16_t *>(Cm), Dskip,                   \
-      static_cast<const uint16_t *>(z), static_cast<uint16_t *>(out), Dm, L
-  if (dtype == NB200_BF16) selective_scan_kernel<NB200_BF16><<<grid, block, 0, st>>>(NB200_SCAN_ARGS);
-  else if (dtype == NB200_F16) selective_scan_kernel<NB200_F16><<<grid, block, 0, st>>>(NB200_SCAN_ARGS);
+  int dev = 0, sms = 0;
+  NB200_CHECK_CUDA(cudaGetDevice(&dev));
+  NB200_CHECK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  const int npt = states_per_thread((long long)B * (Dm / kDB), sms);
+#define NB200_SCAN(DTV)                                                                         \
+  switch (npt) {                                                                                \
+    case 8: launch_scan<DTV, 8>(u, delta, A, Bm, Cm, Dskip, z, out, B, Dm, L, st); break;       \
+    case 4: launch_scan<DTV, 4>(u, delta, A, Bm, Cm, Dskip, z, out, B, Dm, L, st); break;       \
+    default: launch_scan<DTV, 2>(u, delta, A, Bm, Cm, Dskip, z, out, B, Dm, L, st); break;      \
+  }
+  if (dtype == NB200_BF16) { NB200_SCAN(NB200_BF16) }
+  else if (dtype == NB200_F16) { NB200_SCAN(NB200_F16) }
   else return fail(NB200_ERR_UNSUPPORTED, "selective_scan: dtype %d (f16 and bf16 only)", dtype);
-#undef NB200_SCAN_ARGS
+#undef NB200_SCAN
   NB200_CHECK_CUDA(cudaGetLastError());
   return NB200_OK;
 }

@@ -135,6 +135,22 @@ def test_selective_scan_small(cuda, native_lib, dtype, name):
     assert_rms_close(out, ref, 2.0 ** -8)
 
 
+def test_selective_scan_mid_size_takes_four_states_per_thread(cuda, native_lib):
+    """B=4, D=4096, L=128: 512 CTAs, the size at which the launcher picks 4 states per thread on a 148-SM GPU
+    (the small cases above take 2, the full configuration 8); sampled channels against the oracle."""
+    from neptune_mlir import runtime
+
+    B, Dm, L, N = 4, 4096, 128, 16
+    args = inputs.selective_scan_inputs(B=B, Dm=Dm, L=L, N=N, dtype=torch.bfloat16)
+    out = torch.full((B, Dm, L), float("nan"), dtype=torch.bfloat16, device=cuda)
+    runtime.selective_scan(*(a.to(cuda) for a in args), out, B=B, Dm=Dm, L=L, N=N, dtype="bf16")
+    finish()
+    assert bool(torch.isfinite(out.float()).all())
+    ref = selective_scan.selective_scan_reference(*args)
+    assert_storage_close(out, ref, BF16_ATOL, BF16_ULP, scale_by_rms=True)
+    assert_rms_close(out, ref, 2.0 ** -8)
+
+
 def test_selective_scan_config4_full_size_sampled(cuda, native_lib):
     """B=8, D=4096, L=4096, N=16: channels are independent, so a sample of them is checked in full."""
     B, Dm, L, N = 8, 4096, 4096, 16
