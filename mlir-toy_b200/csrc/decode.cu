@@ -5,7 +5,10 @@
 //   * one CTA per (split, kv head, sequence); the G query heads that share a kv head are all
 //     evaluated by the same CTA, so each K/V row is read once and used G times;
 //   * a K/V row of 128 elements is 16 lanes x 16 bytes; a warp therefore reads two rows per load
-//     instruction and keeps 4 K and 4 V loads in flight (8 rows per warp iteration);
+//     instruction, 8 rows per warp iteration.  For the group size of the benchmark configuration
+//     (G = 4) and splits of 256 rows or more the rows come through a ring of shared-memory stages
+//     filled by TMA bulk copies (decode_splitk_ring_kernel); otherwise by 128-bit global loads, four
+//     of K and four of V in flight per lane;
 //   * the 16-lane dot-product reduction is a butterfly that leaves head g's score on lanes whose
 //     bits 3:2 equal g (5 shuffles for G = 4 instead of 16), the online softmax runs on those lanes,
 //     and the probabilities are broadcast back for the PV accumulation;
@@ -15,6 +18,7 @@
 #include <mutex>
 
 #include "nb200_common.cuh"
+#include "sm100_primitives.cuh"
 
 namespace nb200 {
 namespace {
@@ -265,6 +269,254 @@ decode_splitk_kernel(const uint16_t *__restrict__ q, const uint16_t *__restrict_
   }
 }
 
+// ---- G = 4, K/V staged by bulk copies ------------------------------------------------------------
+// Same arithmetic as decode_splitk_kernel<DT, 4>, but the K and V rows of a split arrive through a ring of
+// shared-memory stages filled by TMA bulk copies (one producer thread, mbarrier completion) instead of
+// per-lane global loads.  With plain loads a warp has one iteration (4 KB) in flight and none while it
+// computes; halving the resident warps cost 60 % of the bandwidth, i.e. the kernel was bound by bytes in
+// flight.  The ring keeps three 32 KB stages (64 rows of K and of V) per CTA in flight whatever the warps do.
+constexpr int kRingStages = 3;
+constexpr int kStageRows = 64;
+constexpr int kStageBytes = kStageRows * kHeadDim * 2;                 // 16 KB per operand
+constexpr int kRingThreads = kDecodeThreads + 32;                      // 8 consumer warps + the producer warp
+constexpr int kRingSmem = kRingStages * 2 * kStageBytes + 128;         // stages, then the barriers
+
+struct RingBarriers {
+  uint64_t full[kRingStages], empty[kRingStages];
+  int abort_flag;
+};
+
+__device__ __forceinline__ void bulk_load(uint32_t smem_dst, const void *gsrc, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_dst), "l"(gsrc), "r"(bytes), "r"(bar)
+               : "memory");
+}
+
+template <int DT>
+__global__ void __launch_bounds__(kRingThreads, 2)
+decode_splitk_ring_kernel(const uint16_t *__restrict__ q, const uint16_t *__restrict__ k,
+                          const uint16_t *__restrict__ v, float *__restrict__ partials, int Hkv, int Lkv,
+                          int n_splits, float scale_log2) {
+  constexpr int G = 4;
+  extern __shared__ __align__(128) unsigned char ring[];
+  RingBarriers *bars = reinterpret_cast<RingBarriers *>(ring + kRingStages * 2 * kStageBytes);
+  volatile int *abort_flag = &bars->abort_flag;
+  const uint32_t ring_base = sm100::smem_u32(ring);
+  const uint32_t b_full = sm100::smem_u32(&bars->full[0]), b_empty = sm100::smem_u32(&bars->empty[0]);
+
+  const int split = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
+  const int Hq = Hkv * G;
+  const int t0 = static_cast<int>((long long)split * Lkv / n_splits);
+  const int T = static_cast<int>((long long)(split + 1) * Lkv / n_splits) - t0;
+  const int n_iter = (T + kStageRows - 1) / kStageRows;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int half = lane >> 4, c = lane & 15;
+
+  if (threadIdx.x == 0) {
+    bars->abort_flag = 0;
+    for (int s = 0; s < kRingStages; ++s) {
+      sm100::mbar_init(b_full + 8 * s, 1);
+      sm100::mbar_init(b_empty + 8 * s, kDecodeWarps);
+    }
+    sm100::fence_barrier_init();
+  }
+  __syncthreads();
+
+  uint64_t o2[G][4];
+#pragma unroll
+  for (int g = 0; g < G; ++g)
+#pragma unroll
+    for (int p = 0; p < 4; ++p) o2[g][p] = 0ull;
+  float m_run = -INFINITY, l_run = 0.f;
+  bool ok = true;
+
+  if (warp == kDecodeWarps) {
+    // ================================ producer ================================
+    if (lane == 0) {
+      const size_t kv_base = (((size_t)b * Hkv + hkv) * Lkv + (size_t)t0) * kHeadDim;
+      int issued = 0;
+      for (int it = 0; it < n_iter; ++it) {
+        const int st = it % kRingStages;
+        if (it >= kRingStages && !sm100::mbar_wait(b_empty + 8 * st, ((it / kRingStages) & 1) ^ 1, abort_flag)) break;
+        const int rows = min(kStageRows, T - it * kStageRows);
+        const uint32_t bytes = static_cast<uint32_t>(rows) * kHeadDim * 2;
+        sm100::mbar_arrive_expect_tx(b_full + 8 * st, 2 * bytes);
+        const size_t off = kv_base + (size_t)it * kStageRows * kHeadDim;
+        bulk_load(ring_base + st * 2 * kStageBytes, k + off, bytes, b_full + 8 * st);
+        bulk_load(ring_base + st * 2 * kStageBytes + kStageBytes, v + off, bytes, b_full + 8 * st);
+        ++issued;
+      }
+      if (issued < n_iter) {  // gave up: let the copies in flight land before the CTA's shared memory goes away
+        for (int spin = 0; spin < 100000; ++spin) {
+          bool done = true;
+          for (int n = 0; n < kRingStages; ++n) {
+            const int it = issued - 1 - n;
+            if (it >= 0) done = done && sm100::mbar_try_wait(b_full + 8 * (it % kRingStages), (it / kRingStages) & 1);
+          }
+          if (done) break;
+          __nanosleep(100);
+        }
+      }
+    }
+  } else {
+    // ================================ consumers ===============================
+    // q for the 4 heads of this kv head, this lane's 8 elements, pre-multiplied by the scale.
+    uint64_t q2[G][4];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      const uint4 w = *reinterpret_cast<const uint4 *>(q + ((size_t)b * Hq + hkv * G + g) * kHeadDim + c * 8);
+      const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+      for (int p = 0; p < 4; ++p) {
+        const float2 f = unpack2<DT>(ws[p]);
+        q2[g][p] = f2_pack(f.x * scale_log2, f.y * scale_log2);
+      }
+    }
+    const bool b3 = lane & 8, b2 = lane & 4;
+    for (int it = 0; it < n_iter; ++it) {
+      const int st = it % kRingStages;
+      ok = __all_sync(0xffffffffu, sm100::mbar_wait(b_full + 8 * st, (it / kRingStages) & 1, abort_flag));
+      if (!ok) break;
+      const unsigned char *sk = ring + st * 2 * kStageBytes + (warp * (kPairs * 2) + half) * (kHeadDim * 2) + c * 16;
+      const unsigned char *sv = sk + kStageBytes;
+      const int r0 = it * kStageRows + warp * (kPairs * 2) + half;
+
+      // ---- scores: partial dot products over this lane's 8 elements ----
+      bool valid[kPairs];
+      float part[kPairs][G];
+#pragma unroll
+      for (int i = 0; i < kPairs; ++i) {
+        valid[i] = r0 + 2 * i < T;
+        uint4 kr = *reinterpret_cast<const uint4 *>(sk + i * (2 * kHeadDim * 2));
+        if (!valid[i]) kr = make_uint4(0, 0, 0, 0);   // rows past the end of the split were not copied
+        const uint32_t ws[4] = {kr.x, kr.y, kr.z, kr.w};
+        uint64_t k2[4];
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+          const float2 f = unpack2<DT>(ws[p]);
+          k2[p] = f2_pack(f.x, f.y);
+        }
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+          uint64_t acc = f2_mul(q2[g][0], k2[0]);
+#pragma unroll
+          for (int p = 1; p < 4; ++p) acc = f2_fma(q2[g][p], k2[p], acc);
+          const float2 a = f2_unpack(acc);
+          part[i][g] = a.x + a.y;
+        }
+      }
+      // Butterfly over the 16 lanes of a row: afterwards lanes with bits 3:2 == g hold head g.
+      float sc[kPairs];
+#pragma unroll
+      for (int i = 0; i < kPairs; ++i) {
+        float a0 = b3 ? part[i][2] : part[i][0];
+        float a1 = b3 ? part[i][3] : part[i][1];
+        const float s0 = b3 ? part[i][0] : part[i][2];
+        const float s1 = b3 ? part[i][1] : part[i][3];
+        a0 += __shfl_xor_sync(0xffffffffu, s0, 8);
+        a1 += __shfl_xor_sync(0xffffffffu, s1, 8);
+        float x = b2 ? a1 : a0;
+        const float sx = b2 ? a0 : a1;
+        x += __shfl_xor_sync(0xffffffffu, sx, 4);
+        x += __shfl_xor_sync(0xffffffffu, x, 2);
+        x += __shfl_xor_sync(0xffffffffu, x, 1);
+        sc[i] = valid[i] ? x : -INFINITY;
+      }
+      float mb = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
+      mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, 16));
+      const float m_new = fmaxf(m_run, mb);
+      const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
+      const float a = ex2(m_run - m_safe);
+      float pr[kPairs], psum = 0.f;
+#pragma unroll
+      for (int i = 0; i < kPairs; ++i) {
+        pr[i] = ex2(sc[i] - m_safe);
+        psum += pr[i];
+      }
+      l_run = l_run * a + psum;
+      m_run = m_new;
+
+      // ---- o = o * alpha + sum_i p_i v_i ----
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        const float ag = __shfl_sync(0xffffffffu, a, g << 2);
+        const uint64_t a2 = f2_pack(ag, ag);
+#pragma unroll
+        for (int p = 0; p < 4; ++p) o2[g][p] = f2_mul(o2[g][p], a2);
+      }
+#pragma unroll
+      for (int i = 0; i < kPairs; ++i) {
+        uint4 vr = *reinterpret_cast<const uint4 *>(sv + i * (2 * kHeadDim * 2));
+        if (!valid[i]) vr = make_uint4(0, 0, 0, 0);
+        const uint32_t ws[4] = {vr.x, vr.y, vr.z, vr.w};
+        uint64_t v2[4];
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+          const float2 f = unpack2<DT>(ws[p]);
+          v2[p] = f2_pack(f.x, f.y);
+        }
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+          const float pg = __shfl_sync(0xffffffffu, pr[i], (lane & 16) | (g << 2));
+          const uint64_t p2 = f2_pack(pg, pg);
+#pragma unroll
+          for (int p = 0; p < 4; ++p) o2[g][p] = f2_fma(p2, v2[p], o2[g][p]);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) sm100::mbar_arrive(b_empty + 8 * st);   // this warp is done with its rows of the stage
+    }
+  }
+
+  // ---- merge the two row halves of a warp, then the warps of the CTA (the ring is dead: reuse it) ----
+  __syncthreads();
+  float(*sm_o)[G][kHeadDim] = reinterpret_cast<float(*)[G][kHeadDim]>(ring);
+  float(*sm_m)[G] = reinterpret_cast<float(*)[G]>(ring + kDecodeWarps * G * kHeadDim * 4);
+  float(*sm_l)[G] = sm_m + kDecodeWarps;
+  if (warp < kDecodeWarps) {
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+#pragma unroll
+      for (int p = 0; p < 4; ++p) {
+        float2 f = f2_unpack(o2[g][p]);
+        f.x += __shfl_xor_sync(0xffffffffu, f.x, 16);
+        f.y += __shfl_xor_sync(0xffffffffu, f.y, 16);
+        if (half == 0) {
+          sm_o[warp][g][c * 8 + 2 * p] = f.x;
+          sm_o[warp][g][c * 8 + 2 * p + 1] = f.y;
+        }
+      }
+    }
+    const float l_tot = l_run + __shfl_xor_sync(0xffffffffu, l_run, 16);
+    if (half == 0 && (lane & 3) == 0) {
+      // a wait that expired poisons the partial: the combine then yields NaN instead of a wrong number
+      sm_m[warp][lane >> 2] = ok ? m_run : 0.f;
+      sm_l[warp][lane >> 2] = ok ? l_tot : __int_as_float(0x7fc00000);
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * kHeadDim; idx += kRingThreads) {
+    const int g = idx / kHeadDim, d = idx % kHeadDim;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kDecodeWarps; ++w) M = fmaxf(M, sm_m[w][g]);
+    const float Ms = (M == -INFINITY) ? 0.f : M;
+    float acc = 0.f, lsum = 0.f;
+#pragma unroll
+    for (int w = 0; w < kDecodeWarps; ++w) {
+      const float wgt = ex2(sm_m[w][g] - Ms);
+      acc += wgt * sm_o[w][g][d];
+      lsum += wgt * sm_l[w][g];
+    }
+    float *dst = partials + (((size_t)b * Hq + hkv * G + g) * n_splits + split) * (kHeadDim + 2);
+    dst[d] = acc;
+    if (d == 0) {
+      dst[kHeadDim] = M;
+      dst[kHeadDim + 1] = lsum;
+    }
+  }
+}
+
 // One warp per output row; lane handles 4 of the 128 elements.
 template <int ODT>
 __global__ void __launch_bounds__(128)
@@ -319,7 +571,16 @@ int launch_splitk(const void *q, const void *k, const void *v, float *partials, 
   switch (Hq / Hkv) {
     case 1: decode_splitk_kernel<DT, 1><<<grid, block, 0, st>>>(qp, kp, vp, partials, Hkv, Lkv, n_splits, scale_log2); break;
     case 2: decode_splitk_kernel<DT, 2><<<grid, block, 0, st>>>(qp, kp, vp, partials, Hkv, Lkv, n_splits, scale_log2); break;
-    case 4: decode_splitk_kernel<DT, 4><<<grid, block, 0, st>>>(qp, kp, vp, partials, Hkv, Lkv, n_splits, scale_log2); break;
+    case 4:
+      if (Lkv / n_splits >= 4 * kStageRows) {  // long splits: K/V through the ring of bulk copies
+        NB200_CHECK_CUDA(cudaFuncSetAttribute(decode_splitk_ring_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingSmem));
+        NB200_CHECK_CUDA(cudaFuncSetAttribute(decode_splitk_ring_kernel<DT>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                              cudaSharedmemCarveoutMaxShared));
+        decode_splitk_ring_kernel<DT><<<grid, dim3(kRingThreads), kRingSmem, st>>>(qp, kp, vp, partials, Hkv, Lkv, n_splits, scale_log2);
+      } else {
+        decode_splitk_kernel<DT, 4><<<grid, block, 0, st>>>(qp, kp, vp, partials, Hkv, Lkv, n_splits, scale_log2);
+      }
+      break;
     case 8: decode_splitk_kernel<DT, 8><<<grid, block, 0, st>>>(qp, kp, vp, partials, Hkv, Lkv, n_splits, scale_log2); break;
     default: return fail(NB200_ERR_UNSUPPORTED, "decode: Hq/Hkv = %d not in {1,2,4,8}", Hq / Hkv);
   }

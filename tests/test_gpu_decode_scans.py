@@ -69,6 +69,27 @@ def test_decode_splits_that_do_not_divide_the_length(cuda, native_lib):
     torch.testing.assert_close(p[..., :D], o, rtol=1e-3, atol=2e-3)
 
 
+@pytest.mark.parametrize("dtype,name,atol", [(torch.bfloat16, "bf16", 2e-2), (torch.float16, "f16", 2e-3)])
+def test_decode_long_ragged_splits_through_the_bulk_copy_ring(cuda, native_lib, dtype, name, atol):
+    """Splits of 333/334 rows: long enough for the ring of TMA bulk copies, not a multiple of its 64-row stages,
+    and with a last stage that is only partly filled."""
+    from neptune_mlir import runtime
+
+    B, Hq, Hkv, L, D, S = 2, 8, 2, 1000, 128, 3
+    q, k, v = inputs.decode_inputs(B=B, Hq=Hq, Hkv=Hkv, L=L, D=D, dtype=dtype)
+    partials = torch.full((B, Hq, S, D + 2), float("nan"), device=cuda)
+    out = torch.full((B, Hq, D), float("nan"), dtype=dtype, device=cuda)
+    runtime.decode_splitk(q.to(cuda), k.to(cuda), v.to(cuda), partials, out, B=B, Hq=Hq, Hkv=Hkv, L=L, D=D,
+                          n_splits=S, dtype=name, scale_log2=LOG2E / math.sqrt(D))
+    finish()
+    assert_storage_close(out, decode.decode_reference(q, k, v), atol)
+    m, l, o = decode.decode_partials(q, k, v, S)
+    p = partials.cpu()
+    torch.testing.assert_close(p[..., D] / LOG2E, m, rtol=1e-4, atol=1e-4)
+    torch.testing.assert_close(p[..., D + 1], l, rtol=1e-3, atol=1e-3)
+    torch.testing.assert_close(p[..., :D], o, rtol=1e-3, atol=2e-3)
+
+
 def test_combine_with_gather_strides_and_partial_output(cuda, native_lib):
     """The cross-GPU merge: per-rank partials laid out [rank, rows, D+2] merge to the same answer."""
     from neptune_mlir import runtime
