@@ -5,10 +5,9 @@
 //   * one CTA per (split, kv head, sequence); the G query heads that share a kv head are all
 //     evaluated by the same CTA, so each K/V row is read once and used G times;
 //   * a K/V row of 128 elements is 16 lanes x 16 bytes; a warp therefore reads two rows per load
-//     instruction, 8 rows per warp iteration.  For the group size of the benchmark configuration
-//     (G = 4) and splits of 256 rows or more the rows come through a ring of shared-memory stages
-//     filled by TMA bulk copies (decode_splitk_ring_kernel); otherwise by 128-bit global loads, four
-//     of K and four of V in flight per lane;
+//     instruction, 8 rows per warp iteration.  For splits of 256 rows or more the rows come through
+//     a ring of shared-memory stages filled by TMA bulk copies (decode_splitk_ring_kernel);
+//     otherwise by 128-bit global loads, four of K and four of V in flight per lane;
 //   * the 16-lane dot-product reduction is a butterfly that leaves head g's score on lanes whose
 //     bits 3:2 equal g (5 shuffles for G = 4 instead of 16), the online softmax runs on those lanes,
 //     and the probabilities are broadcast back for the PV accumulation;
@@ -269,8 +268,8 @@ decode_splitk_kernel(const uint16_t *__restrict__ q, const uint16_t *__restrict_
   }
 }
 
-// ---- G = 4, K/V staged by bulk copies ------------------------------------------------------------
-// Same arithmetic as decode_splitk_kernel<DT, 4>, but the K and V rows of a split arrive through a ring of
+// ---- K/V staged by bulk copies --------------------------------------------------------------------
+// Same arithmetic as decode_splitk_kernel, but the K and V rows of a split arrive through a ring of
 // shared-memory stages filled by TMA bulk copies (one producer thread, mbarrier completion) instead of
 // per-lane global loads.  With plain loads a warp has one iteration (4 KB) in flight and none while it
 // computes; halving the resident warps cost 60 % of the bandwidth, i.e. the kernel was bound by bytes in
@@ -292,12 +291,11 @@ __device__ __forceinline__ void bulk_load(uint32_t smem_dst, const void *gsrc, u
                : "memory");
 }
 
-template <int DT>
-__global__ void __launch_bounds__(kRingThreads, 2)
+template <int DT, int G>
+__global__ void __launch_bounds__(kRingThreads, (G >= 8 ? 1 : 2))
 decode_splitk_ring_kernel(const uint16_t *__restrict__ q, const uint16_t *__restrict__ k,
                           const uint16_t *__restrict__ v, float *__restrict__ partials, int Hkv, int Lkv,
                           int n_splits, float scale_log2) {
-  constexpr int G = 4;
   extern __shared__ __align__(128) unsigned char ring[];
   RingBarriers *bars = reinterpret_cast<RingBarriers *>(ring + kRingStages * 2 * kStageBytes);
   volatile int *abort_flag = &bars->abort_flag;
@@ -327,7 +325,14 @@ decode_splitk_ring_kernel(const uint16_t *__restrict__ q, const uint16_t *__rest
   for (int g = 0; g < G; ++g)
 #pragma unroll
     for (int p = 0; p < 4; ++p) o2[g][p] = 0ull;
-  float m_run = -INFINITY, l_run = 0.f;
+  // Running max / sum: for G = 4 of the head this lane owns after the butterfly (head = lane bits 3:2);
+  // for other G every lane tracks all heads.
+  float m_run[G == 4 ? 1 : G], l_run[G == 4 ? 1 : G];
+#pragma unroll
+  for (int g = 0; g < (G == 4 ? 1 : G); ++g) {
+    m_run[g] = -INFINITY;
+    l_run[g] = 0.f;
+  }
   bool ok = true;
 
   if (warp == kDecodeWarps) {
@@ -360,7 +365,7 @@ decode_splitk_ring_kernel(const uint16_t *__restrict__ q, const uint16_t *__rest
     }
   } else {
     // ================================ consumers ===============================
-    // q for the 4 heads of this kv head, this lane's 8 elements, pre-multiplied by the scale.
+    // q for the G heads of this kv head, this lane's 8 elements, pre-multiplied by the scale.
     uint64_t q2[G][4];
 #pragma unroll
     for (int g = 0; g < G; ++g) {
@@ -405,42 +410,78 @@ decode_splitk_ring_kernel(const uint16_t *__restrict__ q, const uint16_t *__rest
           part[i][g] = a.x + a.y;
         }
       }
-      // Butterfly over the 16 lanes of a row: afterwards lanes with bits 3:2 == g hold head g.
-      float sc[kPairs];
+      float pg[kPairs][G];  // probabilities of every head for this lane's rows
+      float alpha[G];
+      if constexpr (G == 4) {
+        // Butterfly over the 16 lanes of a row: afterwards lanes with bits 3:2 == g hold head g.
+        float sc[kPairs];
 #pragma unroll
-      for (int i = 0; i < kPairs; ++i) {
-        float a0 = b3 ? part[i][2] : part[i][0];
-        float a1 = b3 ? part[i][3] : part[i][1];
-        const float s0 = b3 ? part[i][0] : part[i][2];
-        const float s1 = b3 ? part[i][1] : part[i][3];
-        a0 += __shfl_xor_sync(0xffffffffu, s0, 8);
-        a1 += __shfl_xor_sync(0xffffffffu, s1, 8);
-        float x = b2 ? a1 : a0;
-        const float sx = b2 ? a0 : a1;
-        x += __shfl_xor_sync(0xffffffffu, sx, 4);
-        x += __shfl_xor_sync(0xffffffffu, x, 2);
-        x += __shfl_xor_sync(0xffffffffu, x, 1);
-        sc[i] = valid[i] ? x : -INFINITY;
-      }
-      float mb = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
-      mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, 16));
-      const float m_new = fmaxf(m_run, mb);
-      const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
-      const float a = ex2(m_run - m_safe);
-      float pr[kPairs], psum = 0.f;
+        for (int i = 0; i < kPairs; ++i) {
+          float a0 = b3 ? part[i][2] : part[i][0];
+          float a1 = b3 ? part[i][3] : part[i][1];
+          const float s0 = b3 ? part[i][0] : part[i][2];
+          const float s1 = b3 ? part[i][1] : part[i][3];
+          a0 += __shfl_xor_sync(0xffffffffu, s0, 8);
+          a1 += __shfl_xor_sync(0xffffffffu, s1, 8);
+          float x = b2 ? a1 : a0;
+          const float sx = b2 ? a0 : a1;
+          x += __shfl_xor_sync(0xffffffffu, sx, 4);
+          x += __shfl_xor_sync(0xffffffffu, x, 2);
+          x += __shfl_xor_sync(0xffffffffu, x, 1);
+          sc[i] = valid[i] ? x : -INFINITY;
+        }
+        float mb = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
+        mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, 16));
+        const float m_new = fmaxf(m_run[0], mb);
+        const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
+        const float a = ex2(m_run[0] - m_safe);
+        float pr[kPairs], psum = 0.f;
 #pragma unroll
-      for (int i = 0; i < kPairs; ++i) {
-        pr[i] = ex2(sc[i] - m_safe);
-        psum += pr[i];
+        for (int i = 0; i < kPairs; ++i) {
+          pr[i] = ex2(sc[i] - m_safe);
+          psum += pr[i];
+        }
+        l_run[0] = l_run[0] * a + psum;
+        m_run[0] = m_new;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          alpha[g] = __shfl_sync(0xffffffffu, a, g << 2);
+#pragma unroll
+          for (int i = 0; i < kPairs; ++i) pg[i][g] = __shfl_sync(0xffffffffu, pr[i], (lane & 16) | (g << 2));
+        }
+      } else {
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+          float sc[kPairs];
+#pragma unroll
+          for (int i = 0; i < kPairs; ++i) {
+            float x = part[i][g];
+            x += __shfl_xor_sync(0xffffffffu, x, 8);
+            x += __shfl_xor_sync(0xffffffffu, x, 4);
+            x += __shfl_xor_sync(0xffffffffu, x, 2);
+            x += __shfl_xor_sync(0xffffffffu, x, 1);
+            sc[i] = valid[i] ? x : -INFINITY;
+          }
+          float mb = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
+          mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, 16));
+          const float m_new = fmaxf(m_run[g], mb);
+          const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
+          alpha[g] = ex2(m_run[g] - m_safe);
+          float psum = 0.f;
+#pragma unroll
+          for (int i = 0; i < kPairs; ++i) {
+            pg[i][g] = ex2(sc[i] - m_safe);
+            psum += pg[i][g];
+          }
+          l_run[g] = l_run[g] * alpha[g] + psum;
+          m_run[g] = m_new;
+        }
       }
-      l_run = l_run * a + psum;
-      m_run = m_new;
 
       // ---- o = o * alpha + sum_i p_i v_i ----
 #pragma unroll
       for (int g = 0; g < G; ++g) {
-        const float ag = __shfl_sync(0xffffffffu, a, g << 2);
-        const uint64_t a2 = f2_pack(ag, ag);
+        const uint64_t a2 = f2_pack(alpha[g], alpha[g]);
 #pragma unroll
         for (int p = 0; p < 4; ++p) o2[g][p] = f2_mul(o2[g][p], a2);
       }
@@ -457,8 +498,7 @@ decode_splitk_ring_kernel(const uint16_t *__restrict__ q, const uint16_t *__rest
         }
 #pragma unroll
         for (int g = 0; g < G; ++g) {
-          const float pg = __shfl_sync(0xffffffffu, pr[i], (lane & 16) | (g << 2));
-          const uint64_t p2 = f2_pack(pg, pg);
+          const uint64_t p2 = f2_pack(pg[i][g], pg[i][g]);
 #pragma unroll
           for (int p = 0; p < 4; ++p) o2[g][p] = f2_fma(p2, v2[p], o2[g][p]);
         }
@@ -487,11 +527,22 @@ decode_splitk_ring_kernel(const uint16_t *__restrict__ q, const uint16_t *__rest
         }
       }
     }
-    const float l_tot = l_run + __shfl_xor_sync(0xffffffffu, l_run, 16);
-    if (half == 0 && (lane & 3) == 0) {
-      // a wait that expired poisons the partial: the combine then yields NaN instead of a wrong number
-      sm_m[warp][lane >> 2] = ok ? m_run : 0.f;
-      sm_l[warp][lane >> 2] = ok ? l_tot : __int_as_float(0x7fc00000);
+    // a wait that expired poisons the partial: the combine then yields NaN instead of a wrong number
+    if constexpr (G == 4) {
+      const float l_tot = l_run[0] + __shfl_xor_sync(0xffffffffu, l_run[0], 16);
+      if (half == 0 && (lane & 3) == 0) {
+        sm_m[warp][lane >> 2] = ok ? m_run[0] : 0.f;
+        sm_l[warp][lane >> 2] = ok ? l_tot : __int_as_float(0x7fc00000);
+      }
+    } else {
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        const float l_tot = l_run[g] + __shfl_xor_sync(0xffffffffu, l_run[g], 16);
+        if (lane == 0) {
+          sm_m[warp][g] = ok ? m_run[g] : 0.f;
+          sm_l[warp][g] = ok ? l_tot : __int_as_float(0x7fc00000);
+        }
+      }
     }
   }
   __syncthreads();
@@ -568,22 +619,30 @@ int launch_splitk(const void *q, const void *k, const void *v, float *partials, 
   const auto *qp = static_cast<const uint16_t *>(q);
   const auto *kp = static_cast<const uint16_t *>(k);
   const auto *vp = static_cast<const uint16_t *>(v);
+  // long splits: K/V through the ring of bulk copies; short ones: per-lane loads
+  const bool ring = Lkv / n_splits >= 4 * kStageRows;
+#define NB200_DECODE_CASE(GV)                                                                                          \
+  case GV:                                                                                                             \
+    if (ring && GV <= 4) { /* G = 8 keeps 128 accumulator registers per lane: per-lane loads spill less */           \
+      NB200_CHECK_CUDA(cudaFuncSetAttribute(decode_splitk_ring_kernel<DT, GV>,                                         \
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize, kRingSmem));                  \
+      NB200_CHECK_CUDA(cudaFuncSetAttribute(decode_splitk_ring_kernel<DT, GV>,                                         \
+                                            cudaFuncAttributePreferredSharedMemoryCarveout,                            \
+                                            cudaSharedmemCarveoutMaxShared));                                          \
+      decode_splitk_ring_kernel<DT, GV><<<grid, dim3(kRingThreads), kRingSmem, st>>>(qp, kp, vp, partials, Hkv, Lkv,   \
+                                                                                      n_splits, scale_log2);           \
+    } else {                                                                                                           \
+      decode_splitk_kernel<DT, GV><<<grid, block, 0, st>>>(qp, kp, vp, partials, Hkv, Lkv, n_splits, scale_log2);      \
+    }                                                                                                                  \
+    break;
   switch (Hq / Hkv) {
-    case 1: decode_splitk_kernel<DT, 1><<<grid, block, 0, st>>>(qp, kp, vp, partials, Hkv, Lkv, n_splits, scale_log2); break;
-    case 2: decode_splitk_kernel<DT, 2><<<grid, block, 0, st>>>(qp, kp, vp, partials, Hkv, Lkv, n_splits, scale_log2); break;
-    case 4:
-      if (Lkv / n_splits >= 4 * kStageRows) {  // long splits: K/V through the ring of bulk copies
-        NB200_CHECK_CUDA(cudaFuncSetAttribute(decode_splitk_ring_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingSmem));
-        NB200_CHECK_CUDA(cudaFuncSetAttribute(decode_splitk_ring_kernel<DT>, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                              cudaSharedmemCarveoutMaxShared));
-        decode_splitk_ring_kernel<DT><<<grid, dim3(kRingThreads), kRingSmem, st>>>(qp, kp, vp, partials, Hkv, Lkv, n_splits, scale_log2);
-      } else {
-        decode_splitk_kernel<DT, 4><<<grid, block, 0, st>>>(qp, kp, vp, partials, Hkv, Lkv, n_splits, scale_log2);
-      }
-      break;
-    case 8: decode_splitk_kernel<DT, 8><<<grid, block, 0, st>>>(qp, kp, vp, partials, Hkv, Lkv, n_splits, scale_log2); break;
+    NB200_DECODE_CASE(1)
+    NB200_DECODE_CASE(2)
+    NB200_DECODE_CASE(4)
+    NB200_DECODE_CASE(8)
     default: return fail(NB200_ERR_UNSUPPORTED, "decode: Hq/Hkv = %d not in {1,2,4,8}", Hq / Hkv);
   }
+#undef NB200_DECODE_CASE
   NB200_CHECK_CUDA(cudaGetLastError());
   return NB200_OK;
 }
