@@ -100,6 +100,23 @@ int nb200_decode_combine(const float *partials, void *out, int rows, int D, int 
                          long long row_stride, long long split_stride, int out_dtype, void *stream);
 
 /*
+ * Split-K decode over a paged KV cache with per-sequence lengths (no counterpart in the reference): the
+ * serving-side form of nb200_decode_splitk.  A page holds 64 consecutive rows of one sequence for every kv head.
+ *
+ *   q            : [B, Hq, D]
+ *   k_pages, v_pages : [num_pages, Hkv, page_size, D] page pools (f16 or bf16, D == 128, page_size == 64)
+ *   block_table  : int32 [B, max_pages]; entry p of row b is the pool index of page p of sequence b
+ *                  (entries at and beyond ceil(seq_lens[b] / page_size) are not read)
+ *   seq_lens     : int32 [B], rows of each sequence; 0 is allowed and yields a zero output row
+ *   partials     : fp32 [B, Hq, n_splits, D + 2] as for nb200_decode_splitk; merge with nb200_decode_combine
+ * Split s of sequence b covers pages [floor(s*np/n_splits), floor((s+1)*np/n_splits)) with np its page count.
+ * Every page reaches shared memory as one TMA bulk copy per operand.
+ */
+int nb200_decode_paged_splitk(const void *q, const void *k_pages, const void *v_pages, const int *block_table,
+                              const int *seq_lens, float *partials, int B, int Hq, int Hkv, int max_pages,
+                              int page_size, int D, int n_splits, int dtype, float scale_log2, void *stream);
+
+/*
  * Merge of a single-sequence decode whose KV cache is split along its length over the ranks of an
  * NCCL communicator (no counterpart in the reference).  Each rank first runs nb200_decode_splitk on
  * its slice and nb200_decode_combine with out_dtype NB200_F32, which leaves one partial per query

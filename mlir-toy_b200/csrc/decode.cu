@@ -295,7 +295,8 @@ template <int DT, int G>
 __global__ void __launch_bounds__(kRingThreads, (G >= 8 ? 1 : 2))
 decode_splitk_ring_kernel(const uint16_t *__restrict__ q, const uint16_t *__restrict__ k,
                           const uint16_t *__restrict__ v, float *__restrict__ partials, int Hkv, int Lkv,
-                          int n_splits, float scale_log2) {
+                          int n_splits, float scale_log2, const int *__restrict__ block_table,
+                          const int *__restrict__ seq_lens, int max_pages) {
   extern __shared__ __align__(128) unsigned char ring[];
   RingBarriers *bars = reinterpret_cast<RingBarriers *>(ring + kRingStages * 2 * kStageBytes);
   volatile int *abort_flag = &bars->abort_flag;
@@ -304,8 +305,23 @@ decode_splitk_ring_kernel(const uint16_t *__restrict__ q, const uint16_t *__rest
 
   const int split = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
   const int Hq = Hkv * G;
-  const int t0 = static_cast<int>((long long)split * Lkv / n_splits);
-  const int T = static_cast<int>((long long)(split + 1) * Lkv / n_splits) - t0;
+  // Dense cache: split s covers rows [floor(s*L/n), floor((s+1)*L/n)) of a [B, Hkv, L, D] tensor.
+  // Paged cache (block_table != nullptr): a sequence of seq_lens[b] rows lives in pages of 64 rows, page p of it
+  // at pages[block_table[b][p]][hkv]; split s covers whole pages [floor(s*np/n), floor((s+1)*np/n)), and a page is
+  // exactly one stage of the ring.
+  const bool paged = block_table != nullptr;
+  int t0, T;
+  if (paged) {
+    const int len = seq_lens[b];
+    const int np = (len + kStageRows - 1) / kStageRows;
+    const int p0 = static_cast<int>((long long)split * np / n_splits);
+    const int p1 = static_cast<int>((long long)(split + 1) * np / n_splits);
+    t0 = p0 * kStageRows;
+    T = max(0, min(len, p1 * kStageRows) - t0);
+  } else {
+    t0 = static_cast<int>((long long)split * Lkv / n_splits);
+    T = static_cast<int>((long long)(split + 1) * Lkv / n_splits) - t0;
+  }
   const int n_iter = (T + kStageRows - 1) / kStageRows;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int half = lane >> 4, c = lane & 15;
@@ -346,7 +362,11 @@ decode_splitk_ring_kernel(const uint16_t *__restrict__ q, const uint16_t *__rest
         const int rows = min(kStageRows, T - it * kStageRows);
         const uint32_t bytes = static_cast<uint32_t>(rows) * kHeadDim * 2;
         sm100::mbar_arrive_expect_tx(b_full + 8 * st, 2 * bytes);
-        const size_t off = kv_base + (size_t)it * kStageRows * kHeadDim;
+        size_t off = kv_base + (size_t)it * kStageRows * kHeadDim;
+        if (paged) {
+          const int page = block_table[(size_t)b * max_pages + t0 / kStageRows + it];
+          off = ((size_t)page * Hkv + hkv) * kStageRows * kHeadDim;
+        }
         bulk_load(ring_base + st * 2 * kStageBytes, k + off, bytes, b_full + 8 * st);
         bulk_load(ring_base + st * 2 * kStageBytes + kStageBytes, v + off, bytes, b_full + 8 * st);
         ++issued;
@@ -604,7 +624,7 @@ decode_combine_kernel(const float *__restrict__ partials, void *__restrict__ out
       dst[kHeadDim + 1] = lsum;
     }
   } else {
-    const float inv = 1.f / lsum;
+    const float inv = lsum > 0.f ? 1.f / lsum : 0.f;   // a sequence of length 0 (paged cache) yields zeros
     uint2 w;
     w.x = pack2<ODT>(acc.x * inv, acc.y * inv);
     w.y = pack2<ODT>(acc.z * inv, acc.w * inv);
@@ -614,7 +634,8 @@ decode_combine_kernel(const float *__restrict__ partials, void *__restrict__ out
 
 template <int DT>
 int launch_splitk(const void *q, const void *k, const void *v, float *partials, int B, int Hq, int Hkv,
-                  int Lkv, int n_splits, float scale_log2, cudaStream_t st) {
+                  int Lkv, int n_splits, float scale_log2, cudaStream_t st, const int *block_table = nullptr,
+                  const int *seq_lens = nullptr, int max_pages = 0) {
   const dim3 grid(n_splits, Hkv, B), block(kDecodeThreads);
   const auto *qp = static_cast<const uint16_t *>(q);
   const auto *kp = static_cast<const uint16_t *>(k);
@@ -623,14 +644,14 @@ int launch_splitk(const void *q, const void *k, const void *v, float *partials, 
   const bool ring = Lkv / n_splits >= 4 * kStageRows;
 #define NB200_DECODE_CASE(GV)                                                                                          \
   case GV:                                                                                                             \
-    if (ring && GV <= 4) { /* G = 8 keeps 128 accumulator registers per lane: per-lane loads spill less */           \
+    if (block_table != nullptr || (ring && GV <= 4)) { /* dense G = 8: 128 accumulator registers, per-lane loads spill less */ \
       NB200_CHECK_CUDA(cudaFuncSetAttribute(decode_splitk_ring_kernel<DT, GV>,                                         \
                                             cudaFuncAttributeMaxDynamicSharedMemorySize, kRingSmem));                  \
       NB200_CHECK_CUDA(cudaFuncSetAttribute(decode_splitk_ring_kernel<DT, GV>,                                         \
                                             cudaFuncAttributePreferredSharedMemoryCarveout,                            \
                                             cudaSharedmemCarveoutMaxShared));                                          \
-      decode_splitk_ring_kernel<DT, GV><<<grid, dim3(kRingThreads), kRingSmem, st>>>(qp, kp, vp, partials, Hkv, Lkv,   \
-                                                                                      n_splits, scale_log2);           \
+      decode_splitk_ring_kernel<DT, GV><<<grid, dim3(kRingThreads), kRingSmem, st>>>(                                  \
+          qp, kp, vp, partials, Hkv, Lkv, n_splits, scale_log2, block_table, seq_lens, max_pages);                   \
     } else {                                                                                                           \
       decode_splitk_kernel<DT, GV><<<grid, block, 0, st>>>(qp, kp, vp, partials, Hkv, Lkv, n_splits, scale_log2);      \
     }                                                                                                                  \
@@ -674,6 +695,32 @@ extern "C" int nb200_decode_splitk(const void *q, const void *k, const void *v, 
   if (dtype == NB200_BF16) return launch_splitk<NB200_BF16>(q, k, v, partials, B, Hq, Hkv, Lkv, n_splits, scale_log2, st);
   if (dtype == NB200_F16) return launch_splitk<NB200_F16>(q, k, v, partials, B, Hq, Hkv, Lkv, n_splits, scale_log2, st);
   return fail(NB200_ERR_UNSUPPORTED, "decode_splitk: dtype %d (f16 and bf16 only)", dtype);
+}
+
+extern "C" int nb200_decode_paged_splitk(const void *q, const void *k_pages, const void *v_pages,
+                                         const int *block_table, const int *seq_lens, float *partials, int B,
+                                         int Hq, int Hkv, int max_pages, int page_size, int D, int n_splits,
+                                         int dtype, float scale_log2, void *stream) {
+  NB200_REQUIRE(q && k_pages && v_pages && block_table && seq_lens && partials, NB200_ERR_BAD_ARG,
+                "decode_paged_splitk: null pointer");
+  NB200_REQUIRE(B > 0 && Hq > 0 && Hkv > 0 && max_pages > 0 && n_splits > 0, NB200_ERR_BAD_ARG,
+                "decode_paged_splitk: non-positive extent");
+  NB200_REQUIRE(aligned16(q) && aligned16(k_pages) && aligned16(v_pages), NB200_ERR_BAD_ARG,
+                "decode_paged_splitk: q and the page pools must be 16-byte aligned");
+  NB200_REQUIRE(D == kHeadDim, NB200_ERR_UNSUPPORTED, "decode_paged_splitk: D = %d, only 128 is implemented", D);
+  NB200_REQUIRE(page_size == kStageRows, NB200_ERR_UNSUPPORTED,
+                "decode_paged_splitk: page_size = %d, only %d rows per page is implemented", page_size, kStageRows);
+  NB200_REQUIRE(Hq % Hkv == 0, NB200_ERR_UNSUPPORTED, "decode_paged_splitk: Hq %% Hkv != 0");
+  NB200_REQUIRE(Hkv <= 65535 && B <= 65535, NB200_ERR_UNSUPPORTED, "decode_paged_splitk: grid too large");
+  auto st = static_cast<cudaStream_t>(stream);
+  const int Lmax = max_pages * page_size;
+  if (dtype == NB200_BF16)
+    return launch_splitk<NB200_BF16>(q, k_pages, v_pages, partials, B, Hq, Hkv, Lmax, n_splits, scale_log2, st,
+                                     block_table, seq_lens, max_pages);
+  if (dtype == NB200_F16)
+    return launch_splitk<NB200_F16>(q, k_pages, v_pages, partials, B, Hq, Hkv, Lmax, n_splits, scale_log2, st,
+                                    block_table, seq_lens, max_pages);
+  return fail(NB200_ERR_UNSUPPORTED, "decode_paged_splitk: dtype %d (f16 and bf16 only)", dtype);
 }
 
 extern "C" int nb200_decode_combine(const float *partials, void *out, int rows, int D, int n_splits,

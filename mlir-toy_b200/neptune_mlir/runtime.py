@@ -104,6 +104,31 @@ def decode_splitk(q, k, v, partials, out, *, B, Hq, Hkv, L, D, n_splits, dtype, 
         native.check(rc, "nb200_decode_combine")
 
 
+def decode_paged(q, k_pages, v_pages, block_table, seq_lens, partials, out, *, B, Hq, Hkv, max_pages, page_size, D,
+                 n_splits, dtype, scale_log2) -> None:
+    """Split-K decode over a paged KV cache + combine; pools are [num_pages, Hkv, page_size, D]."""
+    _check("q", q, (B, Hq, D), dtype)
+    for name, pool in (("k_pages", k_pages), ("v_pages", v_pages)):
+        if not (isinstance(pool, torch.Tensor) and pool.is_cuda and pool.is_contiguous() and pool.dim() == 4
+                and tuple(pool.shape[1:]) == (Hkv, page_size, D) and pool.dtype == _TORCH_DTYPES[dtype]):
+            raise ValueError(f"{name}: expected a contiguous CUDA [num_pages, {Hkv}, {page_size}, {D}] {dtype} tensor")
+    _check("block_table", block_table, (B, max_pages), torch.int32)
+    _check("seq_lens", seq_lens, (B,), torch.int32)
+    _check("partials", partials, (B, Hq, n_splits, D + 2), torch.float32)
+    _check("out", out, (B, Hq, D), dtype)
+    dev = _same_device(q, k_pages, v_pages, block_table, seq_lens, partials, out)
+    lib = native.lib()
+    with torch.cuda.device(dev):
+        st = _stream(dev)
+        rc = lib.nb200_decode_paged_splitk(q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
+                                           seq_lens.data_ptr(), partials.data_ptr(), B, Hq, Hkv, max_pages, page_size,
+                                           D, n_splits, native.DTYPE_CODES[dtype], float(scale_log2), st)
+        native.check(rc, "nb200_decode_paged_splitk")
+        rc = lib.nb200_decode_combine(partials.data_ptr(), out.data_ptr(), B * Hq, D, n_splits,
+                                      n_splits * (D + 2), D + 2, native.DTYPE_CODES[dtype], st)
+        native.check(rc, "nb200_decode_combine")
+
+
 def decode_combine(partials, out, *, rows, D, n_splits, row_stride, split_stride, out_dtype) -> None:
     """LSE combine with explicit strides (in floats); out_dtype 'f32' writes a partial of D + 2 floats."""
     if not (partials.is_cuda and out.is_cuda and partials.dtype == torch.float32):

@@ -43,6 +43,16 @@ def decode_splitk(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, partials: t
                           n_splits=partials.shape[2], dtype=_name(q), scale_log2=math.log2(math.e) * scale)
 
 
+@torch.library.custom_op("nb200::decode_paged", mutates_args=("partials", "out"))
+def decode_paged(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
+                 seq_lens: torch.Tensor, partials: torch.Tensor, out: torch.Tensor, scale: float) -> None:
+    """Split-K decode over a paged cache: pools [num_pages, Hkv, 64, D], block_table int32 [B, max_pages], seq_lens int32 [B]."""
+    B, Hq, D = q.shape
+    runtime.decode_paged(q, k_pages, v_pages, block_table, seq_lens, partials, out, B=B, Hq=Hq, Hkv=k_pages.shape[1],
+                         max_pages=block_table.shape[1], page_size=k_pages.shape[2], D=D, n_splits=partials.shape[2],
+                         dtype=_name(q), scale_log2=math.log2(math.e) * scale)
+
+
 @torch.library.custom_op("nb200::selective_scan", mutates_args=("out",))
 def selective_scan(u: torch.Tensor, delta: torch.Tensor, A: torch.Tensor, Bm: torch.Tensor, Cm: torch.Tensor,
                    Dskip: torch.Tensor, z: torch.Tensor, out: torch.Tensor) -> None:
@@ -60,4 +70,4 @@ def ssd_chunk_scan(x: torch.Tensor, dt: torch.Tensor, A: torch.Tensor, Bm: torch
                            chunk=chunk, dtype=_name(x))
 
 
-OPS = ("attn_fwd", "decode_splitk", "selective_scan", "ssd_chunk_scan")
+OPS = ("attn_fwd", "decode_splitk", "decode_paged", "selective_scan", "ssd_chunk_scan")

@@ -90,6 +90,44 @@ def test_decode_long_ragged_splits_through_the_bulk_copy_ring(cuda, native_lib, 
     torch.testing.assert_close(p[..., :D], o, rtol=1e-3, atol=2e-3)
 
 
+@pytest.mark.parametrize("Hq,Hkv,n_splits", [(8, 2, 3), (8, 8, 1), (16, 2, 4)])
+def test_decode_over_a_paged_cache_with_ragged_lengths(cuda, native_lib, Hq, Hkv, n_splits):
+    """Pages of 64 rows scattered through a pool, one block table row per sequence, lengths from 0 to 1000
+    (0 rows -> zeros; lengths that end inside a page; fewer pages than splits)."""
+    from neptune_mlir import runtime
+
+    D, page = 128, 64
+    lens = [1000, 0, 1, 63, 64, 65, 500]
+    B, max_pages = len(lens), 16
+    q, k, v = inputs.decode_inputs(B=B, Hq=Hq, Hkv=Hkv, L=max_pages * page, D=D, dtype=torch.bfloat16, config=41)
+    num_pages = B * max_pages + 5
+    gen = torch.Generator().manual_seed(7)
+    perm = torch.randperm(num_pages, generator=gen)[:B * max_pages].view(B, max_pages).to(torch.int32)
+    k_pool = torch.zeros((num_pages, Hkv, page, D), dtype=torch.bfloat16)
+    v_pool = torch.zeros_like(k_pool)
+    for b in range(B):
+        for p in range(max_pages):
+            k_pool[perm[b, p]] = k[b, :, p * page:(p + 1) * page]
+            v_pool[perm[b, p]] = v[b, :, p * page:(p + 1) * page]
+    # entries past a sequence's last page must not be read: poison them
+    table = perm.clone()
+    for b, n in enumerate(lens):
+        table[b, (n + page - 1) // page:] = 2 ** 30
+    partials = torch.full((B, Hq, n_splits, D + 2), float("nan"), device=cuda)
+    out = torch.full((B, Hq, D), float("nan"), dtype=torch.bfloat16, device=cuda)
+    runtime.decode_paged(q.to(cuda), k_pool.to(cuda), v_pool.to(cuda), table.to(cuda),
+                         torch.tensor(lens, dtype=torch.int32, device=cuda), partials, out, B=B, Hq=Hq, Hkv=Hkv,
+                         max_pages=max_pages, page_size=page, D=D, n_splits=n_splits, dtype="bf16",
+                         scale_log2=LOG2E / math.sqrt(D))
+    finish()
+    for b, n in enumerate(lens):
+        if n == 0:
+            assert bool((out[b] == 0).all())
+            continue
+        ref = decode.decode_reference(q[b:b + 1], k[b:b + 1, :, :n], v[b:b + 1, :, :n])
+        assert_storage_close(out[b:b + 1], ref, BF16_ATOL)
+
+
 def test_combine_with_gather_strides_and_partial_output(cuda, native_lib):
     """The cross-GPU merge: per-rank partials laid out [rank, rows, D+2] merge to the same answer."""
     from neptune_mlir import runtime

@@ -83,6 +83,19 @@ def test_nccl_merge_rejects_bad_calls_without_a_gpu(native_lib):
     assert rc == -1
 
 
+def test_paged_decode_rejects_bad_calls_without_a_gpu(native_lib):
+    lib = native.load(str(native_lib))
+    buf = ctypes.create_string_buffer(64)
+    p = ctypes.addressof(buf)
+    p += (-p) % 16
+    rc = lib.nb200_decode_paged_splitk(p, p, p, p, p, p, 2, 8, 2, 16, 32, 128, 4, 1, 0.1, None)
+    assert rc == -2 and b"only 64 rows per page" in lib.nb200_last_error()
+    rc = lib.nb200_decode_paged_splitk(p, p, p, None, p, p, 2, 8, 2, 16, 64, 128, 4, 1, 0.1, None)
+    assert rc == -1
+    rc = lib.nb200_decode_paged_splitk(p, p, p, p, p, p, 2, 8, 3, 16, 64, 128, 4, 1, 0.1, None)
+    assert rc == -2
+
+
 def test_nccl_communicator_argument_checks():
     from neptune_mlir import nccl_comm
     with pytest.raises(ValueError, match="128 bytes"):
