@@ -148,6 +148,21 @@ def decode_splitk_decl(name: str, B: int, Hq: int, Hkv: int, L: int, D: int, n_s
     ], {"htile.operator": "decode_splitk", "n_splits": n_splits, "scale": _f32(1.0 / math.sqrt(D))})
 
 
+def decode_paged_decl(name: str, B: int, Hq: int, Hkv: int, num_pages: int, max_pages: int, D: int, n_splits: int,
+                      page_size: int = 64, dtype: str = "bf16") -> str:
+    """Declaration of split-K decode over a paged KV cache: (q, k_pages, v_pages, block_table, seq_lens, partials, out)."""
+    pool = f"memref<{num_pages}x{Hkv}x{page_size}x{D}x{dtype}>"
+    return _decl(name, [
+        ("q", f"memref<{B}x{Hq}x{D}x{dtype}>"),
+        ("k_pages", pool),
+        ("v_pages", pool),
+        ("block_table", f"memref<{B}x{max_pages}xi32>"),
+        ("seq_lens", f"memref<{B}xi32>"),
+        ("partials", f"memref<{B}x{Hq}x{n_splits}x{D + 2}xf32>"),
+        ("out", f"memref<{B}x{Hq}x{D}x{dtype}>"),
+    ], {"htile.operator": "decode_paged", "n_splits": n_splits, "scale": _f32(1.0 / math.sqrt(D))})
+
+
 def selective_scan_decl(name: str, B: int, Dm: int, L: int, N: int = 16, dtype: str = "bf16") -> str:
     """Declaration of the Mamba-1 selective scan: (u, delta, A, B, C, D, z, out)."""
     seq = f"memref<{B}x{Dm}x{L}x{dtype}>"

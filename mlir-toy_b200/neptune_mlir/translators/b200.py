@@ -199,6 +199,23 @@ class Translator:
             scale = float(fn.attributes.get("scale", 1.0 / math.sqrt(D)))
             return self._runtime_call("decode_splitk", params, B=B, Hq=Hq, Hkv=Hkv, L=L, D=D, n_splits=n_splits,
                                       dtype=dts[0], scale_log2=scale * math.log2(math.e))
+        if operator == "decode_paged":
+            need(len(types) == 7, "expects (q, k_pages, v_pages, block_table, seq_lens, partials, out)")
+            q, kp, vp, table, lens, part, out = shapes
+            need(len(q) == 3 and out == q and len(kp) == 4 and kp == vp, "q/out [B,Hq,D], pools [pages,Hkv,page,D]")
+            B, Hq, D = q
+            Hkv, page = kp[1], kp[2]
+            need(kp[3] == D and Hq % Hkv == 0, "inconsistent extents")
+            need(len(table) == 2 and table[0] == B and lens == (B,) and dts[3] == dts[4] == "i32",
+                 "block_table memref<Bxmax_pagesxi32>, seq_lens memref<Bxi32>")
+            need(len(part) == 4 and part[:2] == (B, Hq) and part[3] == D + 2 and dts[5] == "f32",
+                 "partials must be memref<BxHqxSx(D+2)xf32>")
+            need(dts[0] in ("f16", "bf16") and dts[0] == dts[1] == dts[2] == dts[6], "q/pools/out share f16 or bf16")
+            n_splits = part[2]
+            need(int(fn.attributes.get("n_splits", n_splits)) == n_splits, "n_splits attribute disagrees with partials")
+            scale = float(fn.attributes.get("scale", 1.0 / math.sqrt(D)))
+            return self._runtime_call("decode_paged", params, B=B, Hq=Hq, Hkv=Hkv, max_pages=table[1], page_size=page,
+                                      D=D, n_splits=n_splits, dtype=dts[0], scale_log2=scale * math.log2(math.e))
         if operator == "selective_scan":
             need(len(types) == 8, "expects (u, delta, A, B, C, D, z, out)")
             u, dl, A, Bm, Cm, Dk, z, out = shapes

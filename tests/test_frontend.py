@@ -124,6 +124,22 @@ def test_operator_declarations_check_their_signatures(tmp_path):
         b200.translate_file(str(path))
 
 
+def test_paged_decode_declaration(tmp_path, monkeypatch):
+    text = programs.decode_paged_decl("dp", 7, 8, 2, 117, 16, 128, 3)
+    path = tmp_path / "dp.mlir"
+    path.write_text(text)
+    sources = []
+    for front in ("native", "python"):
+        monkeypatch.setenv("NEPTUNE_HTILE_FRONT", front)
+        sources.append(ast.unparse(b200.translate_file(str(path))))
+    assert sources[0] == sources[1]
+    assert "nb200.decode_paged(ptr_0, ptr_1, ptr_2, ptr_3, ptr_4, ptr_5, ptr_6, B=7, Hq=8, Hkv=2, max_pages=16, " \
+           "page_size=64, D=128, n_splits=3, dtype='bf16'" in sources[0]
+    path.write_text(text.replace("memref<7x16xi32>", "memref<7x16xi64>"))
+    with pytest.raises(NotImplementedError, match="block_table"):
+        b200.translate_file(str(path))
+
+
 def test_syntax_errors_surface_as_runtime_error(tmp_path):
     path = tmp_path / "bad.mlir"
     path.write_text("func.func @f(%a: memref<?x4xf16>) { return }")

@@ -115,10 +115,17 @@ def test_decode_over_a_paged_cache_with_ragged_lengths(cuda, native_lib, Hq, Hkv
         table[b, (n + page - 1) // page:] = 2 ** 30
     partials = torch.full((B, Hq, n_splits, D + 2), float("nan"), device=cuda)
     out = torch.full((B, Hq, D), float("nan"), dtype=torch.bfloat16, device=cuda)
-    runtime.decode_paged(q.to(cuda), k_pool.to(cuda), v_pool.to(cuda), table.to(cuda),
-                         torch.tensor(lens, dtype=torch.int32, device=cuda), partials, out, B=B, Hq=Hq, Hkv=Hkv,
-                         max_pages=max_pages, page_size=page, D=D, n_splits=n_splits, dtype="bf16",
-                         scale_log2=LOG2E / math.sqrt(D))
+    if n_splits == 3:  # once through an emitted module, the way the other operators are called
+        from neptune_mlir import programs
+
+        mod = translate_text(programs.decode_paged_decl("dp", B, Hq, Hkv, num_pages, max_pages, D, n_splits), "paged_dp")
+        mod.dp(q.to(cuda), k_pool.to(cuda), v_pool.to(cuda), table.to(cuda),
+               torch.tensor(lens, dtype=torch.int32, device=cuda), partials, out)
+    else:
+        runtime.decode_paged(q.to(cuda), k_pool.to(cuda), v_pool.to(cuda), table.to(cuda),
+                             torch.tensor(lens, dtype=torch.int32, device=cuda), partials, out, B=B, Hq=Hq, Hkv=Hkv,
+                             max_pages=max_pages, page_size=page, D=D, n_splits=n_splits, dtype="bf16",
+                             scale_log2=LOG2E / math.sqrt(D))
     finish()
     for b, n in enumerate(lens):
         if n == 0:
