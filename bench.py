@@ -39,7 +39,7 @@ for _p in (str(ROOT), str(ROOT / "mlir-toy_b200")):
 import torch  # noqa: E402
 import torch.distributed as dist  # noqa: E402
 
-# ---- the benchmark configurations (BASELINE.json `configs`) ----------------------------------------
+# ---- the benchmark configurations ------------------------------------------------------------------
 ATTN = dict(B=8, H=32, S=4096, D=128)                       # configs[1]: causal bf16 prefill
 DECODE = dict(B=64, Hq=32, Hkv=8, L=32768, D=128, S=16)     # configs[2]
 DECODE1 = dict(B=1, Hq=32, Hkv=8, L=262144, D=128)          # configs[2], single-sequence variant

@@ -42,7 +42,9 @@ def sha(*tensors) -> str:
 
 
 def main() -> None:
-    ref_root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2 and "NEPTUNE_REFERENCE_ROOT" not in os.environ:
+        raise SystemExit(__doc__)
+    ref_root = Path(sys.argv[1] if len(sys.argv) > 1 else os.environ["NEPTUNE_REFERENCE_ROOT"])
     spec = importlib.util.spec_from_file_location(
         "ref_flash_attention_triton", ref_root / "tests" / "golden" / "flash_attention_triton.py")
     mod = importlib.util.module_from_spec(spec)

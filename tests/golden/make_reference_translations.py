@@ -125,7 +125,9 @@ def run_source(source: str, name: str, grid, *tensors) -> None:
 
 
 def main() -> None:
-    ref_root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2 and "NEPTUNE_REFERENCE_ROOT" not in os.environ:
+        raise SystemExit(__doc__)
+    ref_root = Path(sys.argv[1] if len(sys.argv) > 1 else os.environ["NEPTUNE_REFERENCE_ROOT"])
     ref = load_reference_translator(ref_root)
     check_standin(ref, ref_root)
     ref_triton = ref["triton"]

@@ -6,6 +6,7 @@ transposes (:260-263).
 """
 
 import ast
+import os
 from pathlib import Path
 
 import pytest
@@ -18,7 +19,9 @@ from neptune_mlir.translators.common import parse_mlir_module, translate_file_wi
 ROOT = Path(__file__).resolve().parents[1]
 DATA = ROOT / "tests" / "data"
 GOLDEN = ROOT / "tests" / "golden"
-REFERENCE_PROGRAM = Path("/root/reference/tests/data/flash_attention_htile.mlir")
+# the reference project's own program, when its tree is available ($NEPTUNE_REFERENCE_ROOT, else a sibling "reference" directory)
+REFERENCE_ROOT = Path(os.environ.get("NEPTUNE_REFERENCE_ROOT", ROOT.parent / "reference"))
+REFERENCE_PROGRAM = REFERENCE_ROOT / "tests" / "data" / "flash_attention_htile.mlir"
 
 STEMS = sorted(p.stem for p in DATA.glob("*.mlir"))
 
