@@ -59,8 +59,8 @@ const char *nb200_last_error(void);
  *                bounded device-side wait expires the kernel records where in status[0..3] and
  *                finishes without completing the output; read it with nb200_status_read.
  *
- * f16 / bf16 with D == 128 and Sq, Skv multiples of 128 run on tcgen05 tensor cores with TMA-staged
- * tiles; f32 (and any other D <= 256, any Sq/Skv) runs on an exact-fp32 SIMT kernel.
+ * f16 / bf16 with D == 128 (any Sq, Skv) run on tcgen05 tensor cores with TMA-staged tiles; f32 (and any
+ * other D <= 256) runs on an exact-fp32 SIMT kernel.
  */
 int nb200_attn_fwd(const void *q, const void *k, const void *v, void *out,
                    int B, int H, int Sq, int Skv, int D, int dtype,

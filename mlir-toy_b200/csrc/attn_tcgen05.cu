@@ -95,11 +95,13 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
   const int qi = rem / heads_here;
   const int bh = grp * group + rem % heads_here;
   const int qt = causal ? (n_qtiles - 1 - qi) : qi;
-  const int kv_off = Skv - Sq;                                    // causal diagonal offset (multiple of 128)
-  const int last_col = qt * kBM + kv_off + kBM - 1;               // last kv column any row of the tile sees
-  const int nblk = causal ? (last_col / kBN + 1) : (Skv / kBN);
-  const int q_row0 = bh * Sq + qt * kBM;                          // row in the [B*H*Sq, D] view
-  const int kv_row0 = bh * Skv;
+  const int kv_off = Skv - Sq;                                    // causal diagonal offset (>= 0)
+  // last kv column any row of the tile sees; Sq and Skv need not be multiples of the tile sizes: rows and
+  // columns past the end of a (batch, head) slice load as zeros (3-D tensor maps), the columns are masked in
+  // the softmax and the rows are not stored
+  const int last_col = causal ? min(Skv - 1, qt * kBM + kv_off + kBM - 1) : Skv - 1;
+  const int nblk = last_col / kBN + 1;
+  const int q_row0 = qt * kBM;                                    // row inside the (batch, head) slice
 
   if (threadIdx.x == 0) {
     bars->abort_flag = 0;
@@ -149,8 +151,8 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
     // thread that waits for the V buffer first would hold the K load back.
     if (lane == 0) {
       mbar_arrive_expect_tx(b_q_full, kQBytes);
-      tma_load_2d(sQ, &tm_q, 0, q_row0, b_q_full);
-      tma_load_2d(sQ + kQBox, &tm_q, 64, q_row0, b_q_full);
+      tma_load_3d(sQ, &tm_q, 0, q_row0, bh, b_q_full);
+      tma_load_3d(sQ + kQBox, &tm_q, 64, q_row0, bh, b_q_full);
       int issued = 0;
       bool ok = true;
       for (int j = 0; j < nblk && ok; ++j) {
@@ -158,8 +160,8 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         ok = mbar_wait(b_k_empty + 8 * b, ((j >> 1) & 1) ^ 1, abort_flag);
         if (!ok) { report(status, kErrProducer, 2 * j); break; }
         mbar_arrive_expect_tx(b_k_full + 8 * b, kKVBytes);
-        tma_load_2d(sK0 + b * kKVBytes, &tm_k, 0, kv_row0 + j * kBN, b_k_full + 8 * b);
-        tma_load_2d(sK0 + b * kKVBytes + kKVBox, &tm_k, 64, kv_row0 + j * kBN, b_k_full + 8 * b);
+        tma_load_3d(sK0 + b * kKVBytes, &tm_k, 0, j * kBN, bh, b_k_full + 8 * b);
+        tma_load_3d(sK0 + b * kKVBytes + kKVBox, &tm_k, 64, j * kBN, bh, b_k_full + 8 * b);
         ++issued;
       }
       if (!ok) {
@@ -187,8 +189,8 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         ok = mbar_wait(b_v_empty + 8 * b, ((j >> 1) & 1) ^ 1, abort_flag);
         if (!ok) { report(status, kErrProducer, 2 * j + 1); break; }
         mbar_arrive_expect_tx(b_v_full + 8 * b, kKVBytes);
-        tma_load_2d(sV0 + b * kKVBytes, &tm_v, 0, kv_row0 + j * kBN, b_v_full + 8 * b);
-        tma_load_2d(sV0 + b * kKVBytes + kKVBox, &tm_v, 64, kv_row0 + j * kBN, b_v_full + 8 * b);
+        tma_load_3d(sV0 + b * kKVBytes, &tm_v, 0, j * kBN, bh, b_v_full + 8 * b);
+        tma_load_3d(sV0 + b * kKVBytes + kKVBox, &tm_v, 64, j * kBN, bh, b_v_full + 8 * b);
         ++issued;
       }
       if (!ok) {
@@ -302,8 +304,8 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
       tmem_wait_ld();
       tc_fence_before();
       mbar_arrive(b_s_free);
-      // causal: column c of block j is visible to row r iff j*64 + c <= qt*128 + kv_off + r
-      const int vis = causal ? (qt * kBM + kv_off + r - j * kBN) : kBN;  // columns 0..vis are visible
+      // column c of block j exists iff j*64 + c < Skv and, if causal, is visible to row r iff j*64 + c <= qt*128 + kv_off + r
+      const int vis = min(causal ? (qt * kBM + kv_off + r - j * kBN) : kBN, Skv - 1 - j * kBN);  // columns 0..vis are visible
       if (vis < kBN - 1) {
 #pragma unroll
         for (int i = 0; i < kBN; ++i) v[i] = (i > vis) ? 0xff800000u : v[i];  // -inf: 2^(-inf) = 0
@@ -389,7 +391,8 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
     if (ok) {
       tc_fence_after();
       const float inv = 1.f / l;
-      uint16_t *dst = out + (static_cast<size_t>(q_row0) + r) * kD;
+      uint16_t *dst = out + (static_cast<size_t>(bh) * Sq + q_row0 + r) * kD;
+      const bool row_exists = q_row0 + r < Sq;   // the last tile of a slice may be partial
 #pragma unroll 1
       for (int c = 0; c < kD / 32; ++c) {
         uint32_t o[32];
@@ -402,7 +405,7 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
           w.y = pack2<DT>(__uint_as_float(o[8 * i + 2]) * inv, __uint_as_float(o[8 * i + 3]) * inv);
           w.z = pack2<DT>(__uint_as_float(o[8 * i + 4]) * inv, __uint_as_float(o[8 * i + 5]) * inv);
           w.w = pack2<DT>(__uint_as_float(o[8 * i + 6]) * inv, __uint_as_float(o[8 * i + 7]) * inv);
-          *reinterpret_cast<uint4 *>(dst + c * 32 + i * 8) = w;
+          if (row_exists) *reinterpret_cast<uint4 *>(dst + c * 32 + i * 8) = w;
         }
       }
     }
@@ -435,16 +438,16 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
-// [rows, 128] 16-bit row-major tensor, boxes of box_rows rows x 64 columns, 128-byte swizzle.
-int make_tile_map(CUtensorMap *tm, const void *ptr, long long rows, int dtype, int box_rows) {
+// [slices, rows, 128] 16-bit row-major tensor, boxes of 1 slice x box_rows rows x 64 columns, 128-byte swizzle.
+int make_tile_map(CUtensorMap *tm, const void *ptr, long long slices, long long rows, int dtype, int box_rows) {
   EncodeTiledFn enc = encode_tiled_fn();
   NB200_REQUIRE(enc, NB200_ERR_LAUNCH, "attn_fwd: cuTensorMapEncodeTiled is not available from the driver");
-  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(kD), static_cast<cuuint64_t>(rows)};
-  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(kD) * 2};
-  const cuuint32_t box[2] = {64, static_cast<cuuint32_t>(box_rows)};
-  const cuuint32_t estr[2] = {1, 1};
+  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(kD), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(slices)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(kD) * 2, static_cast<cuuint64_t>(rows) * kD * 2};
+  const cuuint32_t box[3] = {64, static_cast<cuuint32_t>(box_rows), 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
   const CUresult r = enc(tm, dtype == NB200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
-                         2, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         3, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   NB200_REQUIRE(r == CUDA_SUCCESS, NB200_ERR_LAUNCH, "attn_fwd: cuTensorMapEncodeTiled failed with code %d", (int)r);
@@ -460,7 +463,7 @@ int launch_tc(const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &t
   // two CTAs of ~97 KB must fit: ask for the largest shared-memory carve-out
   NB200_CHECK_CUDA(cudaFuncSetAttribute(attn_fwd_tcgen05_kernel<DT>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                         cudaSharedmemCarveoutMaxShared));
-  const int n_qtiles = Sq / kBM;
+  const int n_qtiles = (Sq + kBM - 1) / kBM;
   const int group = min(BH, kHeadGroup);
   attn_fwd_tcgen05_kernel<DT><<<dim3(BH * n_qtiles), dim3(kThreads), kSmemBytes, st>>>(
       tq, tk, tv, static_cast<uint16_t *>(out), Sq, Skv, n_qtiles, BH, group, scale_log2, causal, status);
@@ -487,8 +490,8 @@ extern "C" int nb200_attn_fwd(const void *q, const void *k, const void *v, void 
   NB200_REQUIRE(dtype == NB200_F16 || dtype == NB200_BF16 || dtype == NB200_F32, NB200_ERR_UNSUPPORTED,
                 "attn_fwd: dtype %d", dtype);
   auto st = static_cast<cudaStream_t>(stream);
-  const bool tensor_path = (dtype == NB200_F16 || dtype == NB200_BF16) && D == kD && Sq % kBM == 0 &&
-                           Skv % kBM == 0 && (long long)B * H * (Sq / kBM) < (1ll << 31) &&
+  const bool tensor_path = (dtype == NB200_F16 || dtype == NB200_BF16) && D == kD &&
+                           (long long)B * H * ((Sq + kBM - 1) / kBM) < (1ll << 31) &&
                            (long long)B * H * (long long)(Sq > Skv ? Sq : Skv) < (1ll << 31);
   if (!tensor_path) return attn_simt_launch(q, k, v, out, B, H, Sq, Skv, D, dtype, scale_log2, causal, st);
 
@@ -496,9 +499,9 @@ extern "C" int nb200_attn_fwd(const void *q, const void *k, const void *v, void 
                 "attn_fwd: tensors must be 16-byte aligned");
   CUtensorMap tq, tk, tv;
   int rc;
-  if ((rc = make_tile_map(&tq, q, (long long)B * H * Sq, dtype, kBM)) != NB200_OK) return rc;
-  if ((rc = make_tile_map(&tk, k, (long long)B * H * Skv, dtype, kBN)) != NB200_OK) return rc;
-  if ((rc = make_tile_map(&tv, v, (long long)B * H * Skv, dtype, kBN)) != NB200_OK) return rc;
+  if ((rc = make_tile_map(&tq, q, (long long)B * H, Sq, dtype, kBM)) != NB200_OK) return rc;
+  if ((rc = make_tile_map(&tk, k, (long long)B * H, Skv, dtype, kBN)) != NB200_OK) return rc;
+  if ((rc = make_tile_map(&tv, v, (long long)B * H, Skv, dtype, kBN)) != NB200_OK) return rc;
   if (dtype == NB200_BF16)
     return launch_tc<NB200_BF16>(tq, tk, tv, out, B * H, Sq, Skv, scale_log2, causal, status, st);
   return launch_tc<NB200_F16>(tq, tk, tv, out, B * H, Sq, Skv, scale_log2, causal, status, st);

@@ -91,6 +91,14 @@ __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const void *tmap,
       ::"r"(smem_dst), "l"(tmap), "r"(bar), "r"(c0), "r"(c1)
       : "memory");
 }
+// 3-D tiled load: c2 selects the outermost index (here: the (batch, head) slice), so that rows past the end of a
+// slice are out of bounds and arrive as zeros instead of as the next slice's data.
+__device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const void *tmap, int c0, int c1, int c2, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_dst), "l"(tmap), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
 // 2-D tiled store shared -> global (bulk async group of the issuing thread).
 __device__ __forceinline__ void tma_store_2d(const void *tmap, uint32_t smem_src, int c0, int c1) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"

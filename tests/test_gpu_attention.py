@@ -119,6 +119,26 @@ def test_causal_with_longer_kv_and_large_scores(cuda, native_lib):
     assert_storage_close(out, attention.attention_reference(q, k, v, causal=True), BF16_ATOL)
 
 
+@pytest.mark.parametrize("Sq,Skv,causal", [(100, 100, True), (200, 333, True), (129, 1000, False), (1, 77, True),
+                                           (300, 300, False)])
+def test_lengths_that_are_not_multiples_of_the_tiles(cuda, native_lib, Sq, Skv, causal):
+    """Any Sq, Skv on the tensor-core path: partial last tiles, and a neighbouring head full of infinities that
+    must not leak into this head (rows past the end of a slice load as zeros, not as the next slice)."""
+    from neptune_mlir import runtime
+
+    B, H, D = 1, 3, 128
+    q, k, v = inputs.attention_inputs(B, H, Sq, D, torch.bfloat16, config=51, Skv=Skv)
+    k[:, 1] = float("inf")
+    v[:, 1] = float("inf")
+    out = torch.full((B, H, Sq, D), float("nan"), dtype=torch.bfloat16, device=cuda)
+    runtime.attn_fwd(q.to(cuda), k.to(cuda), v.to(cuda), out, shape=(B, H, Sq, D), kv_len=Skv, dtype="bf16",
+                     scale_log2=attention.scale_log2(D), causal=causal)
+    finish()
+    for h in (0, 2):
+        ref = attention.attention_reference(q[:, h:h + 1], k[:, h:h + 1], v[:, h:h + 1], causal=causal)
+        assert_storage_close(out[:, h:h + 1], ref, BF16_ATOL)
+
+
 def test_config2_full_size_sampled(cuda, native_lib):
     """B=8, H=32, S=4096, D=128 bf16 causal; sampled (batch, head, row block) tiles against the oracle."""
     B, H, S, D = 8, 32, 4096, 128
