@@ -59,15 +59,20 @@ const char *nb200_last_error(void);
  *                bounded device-side wait expires the kernel records where in status[0..3] and
  *                finishes without completing the output; read it with nb200_status_read.
  *
- * f16 / bf16 with D == 128 (any Sq, Skv) run on tcgen05 tensor cores with TMA-staged tiles; f32 (and any
- * other D <= 256) runs on an exact-fp32 SIMT kernel.
+ * f16 / bf16 with D == 128 (any Sq, Skv) and 16-byte aligned tensors run on tcgen05 tensor cores with
+ * TMA-staged tiles (misaligned tensors are NB200_ERR_BAD_ARG, not a fall-back); f32, and f16 / bf16 with another
+ * D, run on an exact-fp32 SIMT kernel, which needs D a multiple of 32, D <= 256 and B * H <= 65535 and returns
+ * NB200_ERR_UNSUPPORTED otherwise.
  */
 int nb200_attn_fwd(const void *q, const void *k, const void *v, void *out,
                    int B, int H, int Sq, int Skv, int D, int dtype,
                    float scale_log2, int causal, int *status, void *stream);
 
-/* Copies a status buffer to the host after synchronising `stream`; returns NB200_ERR_DEVICE_TIMEOUT
- * if status[0] != 0, NB200_OK if it is clear. host_out may be NULL. */
+/* Copies a status buffer to the host after synchronising `stream`; returns NB200_OK if status[0] is clear,
+ * NB200_ERR_BAD_ARG if a kernel refused device-side data (code 22: a block-table entry outside the page pool),
+ * NB200_ERR_DEVICE_TIMEOUT for every other code (an expired bounded wait). host_out may be NULL.
+ * A non-zero status[0] makes later attention and SSD launches that are given the same buffer return at once
+ * without touching their outputs, so read it (and zero it) after synchronising whenever a result matters. */
 int nb200_status_read(const int *status, int *host_out, void *stream);
 
 /*
@@ -78,14 +83,28 @@ int nb200_status_read(const int *status, int *host_out, void *stream);
  *   partials : fp32 [B, Hq, n_splits, D + 2]; per (b, hq, split) the un-normalised output o[D]
  *              followed by m (running maximum, exp2 domain) and l (sum of 2^(x - m))
  *   scale_log2 : log2(e) * softmax scale
+ *   status     : device buffer of NB200_STATUS_WORDS int32, zeroed by the caller, or NULL (as for nb200_attn_fwd).
+ *                Long splits stream K/V through a ring of bulk copies whose waits are bounded; a wait that
+ *                expires records code 21 there and poisons that split's partial with NaN, so the combined
+ *                output is NaN rather than a wrong number; nb200_status_read then returns
+ *                NB200_ERR_DEVICE_TIMEOUT.
  * Split s covers KV rows [floor(s*Lkv/n_splits), floor((s+1)*Lkv/n_splits)); n_splits <= Lkv, otherwise free
- * (choose it so that n_splits * Hkv * B fills the GPU's resident CTA slots, two per SM, a whole number of times).
+ * (choose it so that n_splits * Hkv * B fills the GPU's resident CTA slots, two per SM, a whole number of times;
+ * nb200_decode_auto_splits does that).
  */
 size_t nb200_decode_workspace_bytes(int B, int Hq, int D, int n_splits);
 
 int nb200_decode_splitk(const void *q, const void *k, const void *v, float *partials,
                         int B, int Hq, int Hkv, int Lkv, int D, int n_splits, int dtype,
-                        float scale_log2, void *stream);
+                        float scale_log2, int *status, void *stream);
+
+/*
+ * Number of splits that fills the current device's resident CTA slots (two per SM) a whole number of times
+ * for a decode of B sequences with Hkv kv heads of Lkv rows: the smallest count of whole waves whose splits
+ * are at least 256 rows long, at most max_splits (0 = no limit).  Returns 0 on a bad argument or if the device
+ * cannot be queried.  A program whose split count is 0 asks for this choice.
+ */
+int nb200_decode_auto_splits(int B, int Hkv, int Lkv, int max_splits);
 
 /*
  * Log-sum-exp combine of partials.  Partial (row, split) starts at
@@ -95,6 +114,8 @@ int nb200_decode_splitk(const void *q, const void *k, const void *v, float *part
  *   out_dtype NB200_F16 / NB200_BF16 : out is [rows, D], normalised and rounded
  *   out_dtype NB200_F32              : out is [rows, D + 2] fp32, again a partial (o, m, l),
  *                                      ready to be merged once more
+ * partials must be 8-byte aligned with even strides; out 8-byte aligned for 16-bit outputs (it is written four
+ * elements at a time), 4-byte aligned for fp32.
  */
 int nb200_decode_combine(const float *partials, void *out, int rows, int D, int n_splits,
                          long long row_stride, long long split_stride, int out_dtype, void *stream);
@@ -107,14 +128,20 @@ int nb200_decode_combine(const float *partials, void *out, int rows, int D, int 
  *   k_pages, v_pages : [num_pages, Hkv, page_size, D] page pools (f16 or bf16, D == 128, page_size == 64)
  *   block_table  : int32 [B, max_pages]; entry p of row b is the pool index of page p of sequence b
  *                  (entries at and beyond ceil(seq_lens[b] / page_size) are not read)
- *   seq_lens     : int32 [B], rows of each sequence; 0 is allowed and yields a zero output row
+ *   seq_lens     : int32 [B], rows of each sequence; 0 is allowed and yields a zero output row; a length
+ *                  beyond max_pages * page_size is cut to that (the table row addresses no more)
+ *   num_pages    : pages in each pool.  The table lives on the device, so the host cannot check it: the kernel
+ *                  does.  An entry outside [0, num_pages) is never dereferenced; the split that met it gets a
+ *                  NaN partial and `status` (as for nb200_decode_splitk, may be NULL) records code 22 with the
+ *                  offending entry, which nb200_status_read reports as NB200_ERR_BAD_ARG.
  *   partials     : fp32 [B, Hq, n_splits, D + 2] as for nb200_decode_splitk; merge with nb200_decode_combine
  * Split s of sequence b covers pages [floor(s*np/n_splits), floor((s+1)*np/n_splits)) with np its page count.
  * Every page reaches shared memory as one TMA bulk copy per operand.
  */
 int nb200_decode_paged_splitk(const void *q, const void *k_pages, const void *v_pages, const int *block_table,
-                              const int *seq_lens, float *partials, int B, int Hq, int Hkv, int max_pages,
-                              int page_size, int D, int n_splits, int dtype, float scale_log2, void *stream);
+                              const int *seq_lens, float *partials, int B, int Hq, int Hkv, int num_pages,
+                              int max_pages, int page_size, int D, int n_splits, int dtype, float scale_log2,
+                              int *status, void *stream);
 
 /*
  * Merge of a single-sequence decode whose KV cache is split along its length over the ranks of an

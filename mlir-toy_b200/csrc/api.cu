@@ -35,6 +35,9 @@ extern "C" int nb200_status_read(const int *status, int *host_out, void *stream)
   NB200_CHECK_CUDA(cudaMemcpyAsync(host, status, sizeof(host), cudaMemcpyDeviceToHost, st));
   NB200_CHECK_CUDA(cudaStreamSynchronize(st));
   if (host_out) std::memcpy(host_out, host, sizeof(host));
+  if (host[0] == 22)  // the paged decode met a block-table entry outside the pool and did not dereference it
+    return nb200::fail(NB200_ERR_BAD_ARG, "paged decode: block table entry %d is outside the page pool (block %d, thread %d)",
+                       host[2], host[1], host[3]);
   if (host[0] != 0)
     return nb200::fail(NB200_ERR_DEVICE_TIMEOUT,
                        "device-side wait expired: code %d, block %d, detail %d/%d", host[0], host[1],

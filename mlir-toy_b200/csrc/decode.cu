@@ -285,6 +285,17 @@ struct RingBarriers {
   int abort_flag;
 };
 
+// Codes the ring kernel records in status[0] (block, detail and thread follow in status[1..3]).
+enum : int { kErrDecodeWait = 21, kErrDecodeBadPage = 22 };
+
+__device__ __forceinline__ void decode_report(int *status, int code, int detail) {
+  if (status && atomicCAS(status, 0, code) == 0) {
+    status[1] = static_cast<int>(blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z));
+    status[2] = detail;
+    status[3] = static_cast<int>(threadIdx.x);
+  }
+}
+
 __device__ __forceinline__ void bulk_load(uint32_t smem_dst, const void *gsrc, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                ::"r"(smem_dst), "l"(gsrc), "r"(bytes), "r"(bar)
@@ -296,7 +307,7 @@ __global__ void __launch_bounds__(kRingThreads, (G >= 8 ? 1 : 2))
 decode_splitk_ring_kernel(const uint16_t *__restrict__ q, const uint16_t *__restrict__ k,
                           const uint16_t *__restrict__ v, float *__restrict__ partials, int Hkv, int Lkv,
                           int n_splits, float scale_log2, const int *__restrict__ block_table,
-                          const int *__restrict__ seq_lens, int max_pages) {
+                          const int *__restrict__ seq_lens, int max_pages, int num_pages, int *status) {
   extern __shared__ __align__(128) unsigned char ring[];
   RingBarriers *bars = reinterpret_cast<RingBarriers *>(ring + kRingStages * 2 * kStageBytes);
   volatile int *abort_flag = &bars->abort_flag;
@@ -312,7 +323,8 @@ decode_splitk_ring_kernel(const uint16_t *__restrict__ q, const uint16_t *__rest
   const bool paged = block_table != nullptr;
   int t0, T;
   if (paged) {
-    const int len = seq_lens[b];
+    // the table row has max_pages entries: a length beyond that (or a negative one) is cut to what the row can address
+    const int len = max(0, min(seq_lens[b], max_pages * kStageRows));
     const int np = (len + kStageRows - 1) / kStageRows;
     const int p0 = static_cast<int>((long long)split * np / n_splits);
     const int p1 = static_cast<int>((long long)(split + 1) * np / n_splits);
@@ -358,13 +370,23 @@ decode_splitk_ring_kernel(const uint16_t *__restrict__ q, const uint16_t *__rest
       int issued = 0;
       for (int it = 0; it < n_iter; ++it) {
         const int st = it % kRingStages;
-        if (it >= kRingStages && !sm100::mbar_wait(b_empty + 8 * st, ((it / kRingStages) & 1) ^ 1, abort_flag)) break;
+        if (it >= kRingStages && !sm100::mbar_wait(b_empty + 8 * st, ((it / kRingStages) & 1) ^ 1, abort_flag)) {
+          decode_report(status, kErrDecodeWait, it);
+          break;
+        }
         const int rows = min(kStageRows, T - it * kStageRows);
         const uint32_t bytes = static_cast<uint32_t>(rows) * kHeadDim * 2;
         sm100::mbar_arrive_expect_tx(b_full + 8 * st, 2 * bytes);
         size_t off = kv_base + (size_t)it * kStageRows * kHeadDim;
         if (paged) {
           const int page = block_table[(size_t)b * max_pages + t0 / kStageRows + it];
+          if (page < 0 || page >= num_pages) {
+            // a table entry outside the pool: no copy is issued from it; the consumers see the abort flag, the
+            // partial is poisoned and the status words say which entry it was
+            decode_report(status, kErrDecodeBadPage, page);
+            *abort_flag = 1;
+            break;
+          }
           off = ((size_t)page * Hkv + hkv) * kStageRows * kHeadDim;
         }
         bulk_load(ring_base + st * 2 * kStageBytes, k + off, bytes, b_full + 8 * st);
@@ -401,7 +423,10 @@ decode_splitk_ring_kernel(const uint16_t *__restrict__ q, const uint16_t *__rest
     for (int it = 0; it < n_iter; ++it) {
       const int st = it % kRingStages;
       ok = __all_sync(0xffffffffu, sm100::mbar_wait(b_full + 8 * st, (it / kRingStages) & 1, abort_flag));
-      if (!ok) break;
+      if (!ok) {
+        if (lane == 0) decode_report(status, kErrDecodeWait, 1000000 + it);   // no-op if the producer already said why
+        break;
+      }
       const unsigned char *sk = ring + st * 2 * kStageBytes + (warp * (kPairs * 2) + half) * (kHeadDim * 2) + c * 16;
       const unsigned char *sv = sk + kStageBytes;
       const int r0 = it * kStageRows + warp * (kPairs * 2) + half;
@@ -634,8 +659,9 @@ decode_combine_kernel(const float *__restrict__ partials, void *__restrict__ out
 
 template <int DT>
 int launch_splitk(const void *q, const void *k, const void *v, float *partials, int B, int Hq, int Hkv,
-                  int Lkv, int n_splits, float scale_log2, cudaStream_t st, const int *block_table = nullptr,
-                  const int *seq_lens = nullptr, int max_pages = 0) {
+                  int Lkv, int n_splits, float scale_log2, int *status, cudaStream_t st,
+                  const int *block_table = nullptr, const int *seq_lens = nullptr, int max_pages = 0,
+                  int num_pages = 0) {
   const dim3 grid(n_splits, Hkv, B), block(kDecodeThreads);
   const auto *qp = static_cast<const uint16_t *>(q);
   const auto *kp = static_cast<const uint16_t *>(k);
@@ -651,7 +677,7 @@ int launch_splitk(const void *q, const void *k, const void *v, float *partials, 
                                             cudaFuncAttributePreferredSharedMemoryCarveout,                            \
                                             cudaSharedmemCarveoutMaxShared));                                          \
       decode_splitk_ring_kernel<DT, GV><<<grid, dim3(kRingThreads), kRingSmem, st>>>(                                  \
-          qp, kp, vp, partials, Hkv, Lkv, n_splits, scale_log2, block_table, seq_lens, max_pages);                   \
+          qp, kp, vp, partials, Hkv, Lkv, n_splits, scale_log2, block_table, seq_lens, max_pages, num_pages, status); \
     } else {                                                                                                           \
       decode_splitk_kernel<DT, GV><<<grid, block, 0, st>>>(qp, kp, vp, partials, Hkv, Lkv, n_splits, scale_log2);      \
     }                                                                                                                  \
@@ -678,9 +704,38 @@ extern "C" size_t nb200_decode_workspace_bytes(int B, int Hq, int D, int n_split
   return (size_t)B * Hq * n_splits * (D + 2) * sizeof(float);
 }
 
+extern "C" int nb200_decode_auto_splits(int B, int Hkv, int Lkv, int max_splits) {
+  if (B <= 0 || Hkv <= 0 || Lkv <= 0 || max_splits < 0) return 0;
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+    return 0;
+  // One CTA per (split, kv head, sequence), two CTAs resident per SM.  The time of a launch is about
+  // waves * (rows per split + a fixed cost per CTA): pick the split count that minimises it.  The fixed cost
+  // (prologue, cross-warp merge, write of the partial) is worth about 128 rows of streaming at one CTA's
+  // share of the bandwidth.  Splits stay at 256 rows or more (from there K/V stream through the ring of bulk
+  // copies) unless that leaves CTA slots empty, in which case they may shrink to 64 rows.
+  const long long slots = 2ll * sms, units = (long long)B * Hkv;
+  const long long cap = max_splits > 0 ? max_splits : (1ll << 30);
+  long long best = 1;
+  double best_cost = 0.0;
+  for (long long n = 1; n <= cap && n <= Lkv && n <= 4096; ++n) {
+    const long long rows = Lkv / n;
+    if (n > 1 && rows < 4 * kStageRows && ((n - 1) * units >= slots || rows < kStageRows)) break;
+    const long long waves = (n * units + slots - 1) / slots;
+    const double cost = static_cast<double>(waves) * static_cast<double>((Lkv + n - 1) / n + 128);
+    if (n == 1 || cost < best_cost * 0.995) {   // a clearly better count only: more splits cost combine work
+      best = n;
+      best_cost = cost;
+    }
+  }
+  if (best > Lkv) best = Lkv;
+  return static_cast<int>(best);
+}
+
 extern "C" int nb200_decode_splitk(const void *q, const void *k, const void *v, float *partials, int B,
                                    int Hq, int Hkv, int Lkv, int D, int n_splits, int dtype,
-                                   float scale_log2, void *stream) {
+                                   float scale_log2, int *status, void *stream) {
   NB200_REQUIRE(q && k && v && partials, NB200_ERR_BAD_ARG, "decode_splitk: null pointer");
   NB200_REQUIRE(B > 0 && Hq > 0 && Hkv > 0 && Lkv > 0 && n_splits > 0, NB200_ERR_BAD_ARG,
                 "decode_splitk: non-positive extent");
@@ -692,19 +747,21 @@ extern "C" int nb200_decode_splitk(const void *q, const void *k, const void *v, 
                 n_splits, Lkv);
   NB200_REQUIRE(Hkv <= 65535 && B <= 65535, NB200_ERR_UNSUPPORTED, "decode_splitk: grid too large");
   auto st = static_cast<cudaStream_t>(stream);
-  if (dtype == NB200_BF16) return launch_splitk<NB200_BF16>(q, k, v, partials, B, Hq, Hkv, Lkv, n_splits, scale_log2, st);
-  if (dtype == NB200_F16) return launch_splitk<NB200_F16>(q, k, v, partials, B, Hq, Hkv, Lkv, n_splits, scale_log2, st);
+  if (dtype == NB200_BF16) return launch_splitk<NB200_BF16>(q, k, v, partials, B, Hq, Hkv, Lkv, n_splits, scale_log2, status, st);
+  if (dtype == NB200_F16) return launch_splitk<NB200_F16>(q, k, v, partials, B, Hq, Hkv, Lkv, n_splits, scale_log2, status, st);
   return fail(NB200_ERR_UNSUPPORTED, "decode_splitk: dtype %d (f16 and bf16 only)", dtype);
 }
 
 extern "C" int nb200_decode_paged_splitk(const void *q, const void *k_pages, const void *v_pages,
                                          const int *block_table, const int *seq_lens, float *partials, int B,
-                                         int Hq, int Hkv, int max_pages, int page_size, int D, int n_splits,
-                                         int dtype, float scale_log2, void *stream) {
+                                         int Hq, int Hkv, int num_pages, int max_pages, int page_size, int D,
+                                         int n_splits, int dtype, float scale_log2, int *status, void *stream) {
   NB200_REQUIRE(q && k_pages && v_pages && block_table && seq_lens && partials, NB200_ERR_BAD_ARG,
                 "decode_paged_splitk: null pointer");
-  NB200_REQUIRE(B > 0 && Hq > 0 && Hkv > 0 && max_pages > 0 && n_splits > 0, NB200_ERR_BAD_ARG,
+  NB200_REQUIRE(B > 0 && Hq > 0 && Hkv > 0 && num_pages > 0 && max_pages > 0 && n_splits > 0, NB200_ERR_BAD_ARG,
                 "decode_paged_splitk: non-positive extent");
+  NB200_REQUIRE((long long)max_pages * page_size < (1ll << 31), NB200_ERR_UNSUPPORTED,
+                "decode_paged_splitk: max_pages * page_size does not fit 31 bits");
   NB200_REQUIRE(aligned16(q) && aligned16(k_pages) && aligned16(v_pages), NB200_ERR_BAD_ARG,
                 "decode_paged_splitk: q and the page pools must be 16-byte aligned");
   NB200_REQUIRE(D == kHeadDim, NB200_ERR_UNSUPPORTED, "decode_paged_splitk: D = %d, only 128 is implemented", D);
@@ -715,11 +772,11 @@ extern "C" int nb200_decode_paged_splitk(const void *q, const void *k_pages, con
   auto st = static_cast<cudaStream_t>(stream);
   const int Lmax = max_pages * page_size;
   if (dtype == NB200_BF16)
-    return launch_splitk<NB200_BF16>(q, k_pages, v_pages, partials, B, Hq, Hkv, Lmax, n_splits, scale_log2, st,
-                                     block_table, seq_lens, max_pages);
+    return launch_splitk<NB200_BF16>(q, k_pages, v_pages, partials, B, Hq, Hkv, Lmax, n_splits, scale_log2, status, st,
+                                     block_table, seq_lens, max_pages, num_pages);
   if (dtype == NB200_F16)
-    return launch_splitk<NB200_F16>(q, k_pages, v_pages, partials, B, Hq, Hkv, Lmax, n_splits, scale_log2, st,
-                                    block_table, seq_lens, max_pages);
+    return launch_splitk<NB200_F16>(q, k_pages, v_pages, partials, B, Hq, Hkv, Lmax, n_splits, scale_log2, status, st,
+                                    block_table, seq_lens, max_pages, num_pages);
   return fail(NB200_ERR_UNSUPPORTED, "decode_paged_splitk: dtype %d (f16 and bf16 only)", dtype);
 }
 
@@ -732,6 +789,9 @@ extern "C" int nb200_decode_combine(const float *partials, void *out, int rows, 
   NB200_REQUIRE(row_stride % 2 == 0 && split_stride % 2 == 0 &&
                     (reinterpret_cast<uintptr_t>(partials) & 7u) == 0,
                 NB200_ERR_BAD_ARG, "decode_combine: partials must be 8-byte aligned with even strides");
+  // 16-bit outputs are written as 8-byte vectors (four elements per lane), fp32 partials as single floats
+  NB200_REQUIRE((reinterpret_cast<uintptr_t>(out) & (out_dtype == NB200_F32 ? 3u : 7u)) == 0, NB200_ERR_BAD_ARG,
+                "decode_combine: out must be %d-byte aligned", out_dtype == NB200_F32 ? 4 : 8);
   auto st = static_cast<cudaStream_t>(stream);
   const dim3 grid((rows + 3) / 4), block(128);
   switch (out_dtype) {
@@ -781,6 +841,9 @@ extern "C" int nb200_decode_fwd_static(const void *q, const void *k, const void 
   NB200_REQUIRE(q && k && v && out, NB200_ERR_BAD_ARG, "decode_fwd_static: null pointer");
   NB200_REQUIRE(B > 0 && Hq > 0 && Hkv > 0 && Lkv > 0 && D > 0 && n_splits > 0, NB200_ERR_BAD_ARG,
                 "decode_fwd_static: non-positive extent");
+  // checked here as well as in the combine, so that a bad `out` is refused before anything is launched
+  NB200_REQUIRE((reinterpret_cast<uintptr_t>(out) & 7u) == 0, NB200_ERR_BAD_ARG,
+                "decode_fwd_static: out must be 8-byte aligned");
   const size_t need = (size_t)B * Hq * n_splits * ((size_t)D + 2) * sizeof(float);
   NB200_REQUIRE(need <= (size_t)NB200_DECODE_STATIC_SCRATCH_BYTES, NB200_ERR_UNSUPPORTED,
                 "decode_fwd_static: B*Hq*n_splits*(D+2) floats = %zu bytes of partials do not fit the built-in "
@@ -791,7 +854,7 @@ extern "C" int nb200_decode_fwd_static(const void *q, const void *k, const void 
   if (rc != NB200_OK) return rc;
   // Split-K writes every (row, split) slot that the combine reads, so nothing left in the array by
   // an earlier call can leak into this one and nothing has to be cleared first.
-  const int rc1 = nb200_decode_splitk(q, k, v, partials, B, Hq, Hkv, Lkv, D, n_splits, dtype, scale_log2, stream);
+  const int rc1 = nb200_decode_splitk(q, k, v, partials, B, Hq, Hkv, Lkv, D, n_splits, dtype, scale_log2, nullptr, stream);
   if (rc1 != NB200_OK) return rc1;
   return nb200_decode_combine(partials, out, B * Hq, D, n_splits, (long long)n_splits * (D + 2), D + 2, dtype,
                               stream);

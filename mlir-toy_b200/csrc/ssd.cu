@@ -15,12 +15,14 @@
 //   Y += (G o decay o mask) . x              decay_ij = e^(cum_i - cum_j) dt_j for j <= i; A is G
 //                                            overwritten in place as 16-bit in TMEM        (128x64x128)
 //
-//   warps 0-3   thread i = row i of the step = TMEM lane i: prefix sum of dt*A (each warp scans all
-//               128 values itself, so no cross-warp exchange; done a step ahead, while the last
-//               product of the previous step runs), the scaled copies of x and S, the decay/mask
-//               pass over G (an exponential per element only in the 32-column chunk on the
-//               diagonal; chunks left of it take one factor per row and one per column), and the
-//               epilogue (Y -> 16 bit -> staging buffer)
+//   warps 0-3   thread i = row i of the step = TMEM lane i: the scaled copies of x and S, the
+//               decay/mask pass over G (an exponential per element only in the 32-column chunk on
+//               the diagonal; chunks left of it take one factor per row and one per column), and
+//               the epilogue (Y -> 16 bit -> staging buffer)
+//   warp 6      prefix sum of dt*A over the 128 rows of a step and everything derived from it alone
+//               (cum_j, dt_j, cum_j - log2 dt_j, the column factors), written to a double-buffered
+//               table in shared memory one to two steps ahead of the element-wise warps, which
+//               used to spend a quarter of their step on it
 //   warp 4      TMA producer: the C, B and x tiles of the next step, each issued as soon as the
 //               product that last read its buffer has retired, and the TMA store of the finished
 //               Y tile (staged by the element-wise warps in the buffer x occupied).  The two 16 KB
@@ -45,20 +47,23 @@ using namespace sm100;
 constexpr int kQ = 128;          // rows per step
 constexpr int kP = 64;           // head dimension
 constexpr int kN = 128;          // state dimension
-constexpr int kSsdThreads = 192;
+constexpr int kSsdThreads = 224;
 constexpr int kBCBytes = kQ * kN * 2;      // 32 KB: two 64-column boxes of 16 KB
 constexpr int kBCBox = kBCBytes / 2;
 constexpr int kXBytes = kQ * kP * 2;       // 16 KB: one box
 constexpr int kTileBytes = 2 * kBCBytes + kXBytes;
 constexpr int kDtBytes = kQ * 4 * 4;      // 128 rows x 4 heads of dt (fp32): the 16-byte minimum of a TMA box row
-constexpr int kSsdSmem = 2 * kBCBytes + 2 * kXBytes + 4 * 2 * kQ * 4 /*lb, cf*/ + 2 * kDtBytes + 256 /*barriers*/;
+constexpr int kPfFloats = 4 * kQ;        // one prefix table: cum[128] | dt[128] | lb[128] | cf[128]
+constexpr int kPfBytes = kPfFloats * 4;
+constexpr int kSsdSmem = 2 * kBCBytes + 2 * kXBytes + 2 * kPfBytes + 2 * kDtBytes + 256 /*barriers*/;
 constexpr int kSsdTmemCols = 256;
 constexpr float kLog2e = 1.4426950408889634f;
 
-enum : int { kErrSsdProducer = 11, kErrSsdMma = 12, kErrSsdCompute = 13, kErrSsdAlign = 15 };
+enum : int { kErrSsdProducer = 11, kErrSsdMma = 12, kErrSsdCompute = 13, kErrSsdPrefix = 14, kErrSsdAlign = 15 };
 
 struct SsdBarriers {
-  uint64_t c_full, b_full, x_full, z_done, y_staged, y_free, e1a, inter_done, e1b, g_ready, m_ready, y_ready, dt_full[2];
+  uint64_t c_full, b_full, x_full, z_done, y_staged, y_free, e1a, inter_done, e1b, g_ready, m_ready, y_ready, dt_full[2],
+      pf_full[2], pf_free[2];
   uint32_t tmem_base;
   int abort_flag;
   int skip;
@@ -70,15 +75,6 @@ __device__ __forceinline__ void ssd_report(int *status, int code, int detail) {
     status[2] = detail;
     status[3] = static_cast<int>(threadIdx.x);
   }
-}
-
-// A load that stays where it is written: the compiler may neither sink it to its first use nor re-issue it
-// there (it does both with a plain load from a const __restrict__ pointer), which is the point of a prefetch
-// into registers a whole step ahead.
-__device__ __forceinline__ float ldg_pinned(const float *p) {
-  float v;
-  asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(p));
-  return v;
 }
 
 __device__ __forceinline__ float lg2(float x) {
@@ -106,10 +102,10 @@ ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
   // U[(s+1)&1] holds the 16-bit copy of the incoming state, then w*x(s), then (loaded ahead) x(s+1).
   const uint32_t sB = base, sC = base + kBCBytes, sU = base + 2 * kBCBytes;
   unsigned char *pU = smem + 2 * kBCBytes;
-  float *lb_all = reinterpret_cast<float *>(smem + 2 * kBCBytes + 2 * kXBytes);  // [4 warps][lb 128 | cf 128]
-  const float *dt_tile = reinterpret_cast<const float *>(smem + 2 * kBCBytes + 2 * kXBytes + 4 * 2 * kQ * 4);  // [2][128][4]
-  const uint32_t sDt = base + 2 * kBCBytes + 2 * kXBytes + 4 * 2 * kQ * 4;
-  SsdBarriers *bars = reinterpret_cast<SsdBarriers *>(smem + 2 * kBCBytes + 2 * kXBytes + 4 * 2 * kQ * 4 + 2 * kDtBytes);
+  float *pf_all = reinterpret_cast<float *>(smem + 2 * kBCBytes + 2 * kXBytes);  // [2 steps][cum | dt | lb | cf][128]
+  const float *dt_tile = reinterpret_cast<const float *>(smem + 2 * kBCBytes + 2 * kXBytes + 2 * kPfBytes);  // [2][128][4]
+  const uint32_t sDt = base + 2 * kBCBytes + 2 * kXBytes + 2 * kPfBytes;
+  SsdBarriers *bars = reinterpret_cast<SsdBarriers *>(smem + 2 * kBCBytes + 2 * kXBytes + 2 * kPfBytes + 2 * kDtBytes);
   volatile int *abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -134,6 +130,10 @@ ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
     mbar_init(smem_u32(&bars->y_ready), 1);
     mbar_init(smem_u32(&bars->dt_full[0]), 1);
     mbar_init(smem_u32(&bars->dt_full[1]), 1);
+    mbar_init(smem_u32(&bars->pf_full[0]), 1);
+    mbar_init(smem_u32(&bars->pf_full[1]), 1);
+    mbar_init(smem_u32(&bars->pf_free[0]), 128);
+    mbar_init(smem_u32(&bars->pf_free[1]), 128);
     fence_barrier_init();
     fence_proxy_async_smem();
   }
@@ -162,7 +162,8 @@ ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
                  b_y_staged = smem_u32(&bars->y_staged), b_y_free = smem_u32(&bars->y_free), b_e1a = smem_u32(&bars->e1a), b_inter_done = smem_u32(&bars->inter_done),
                  b_e1b = smem_u32(&bars->e1b), b_g_ready = smem_u32(&bars->g_ready),
                  b_m_ready = smem_u32(&bars->m_ready), b_y_ready = smem_u32(&bars->y_ready),
-                 b_dt_full = smem_u32(&bars->dt_full[0]);  // buffer p is at + 8 * p
+                 b_dt_full = smem_u32(&bars->dt_full[0]),  // buffer p is at + 8 * p
+                 b_pf_full = smem_u32(&bars->pf_full[0]), b_pf_free = smem_u32(&bars->pf_free[0]);
 
   if (warp == 4) {
     // ================================ TMA producer ================================
@@ -297,45 +298,33 @@ ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       }
     }
     __syncwarp();
-  } else {
-    // ================================ element-wise warps ==========================
-    const int i = warp * 32 + lane;                           // row of the step == TMEM lane
-    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
-    float *lb = lb_all + warp * 2 * kQ;                        // this warp's copy of cum_j - log2(dt_j)
-    float *cf = lb + kQ;                                       // and of e^(cum_end(j) - cum_j) dt_j, see prefix
+  } else if (warp == 6) {
+    // ================================ prefix warp =================================
+    // Lane l owns rows 4l..4l+3 of the step.  Per step sp it leaves in table sp & 1:
+    //   cum[j]  inclusive prefix sum of dt*A*log2(e) inside the step (cum[127] is the step total, cum[31], cum[63],
+    //           cum[95] are the references of column chunks 0..2)
+    //   dt[j]
+    //   lb[j]   cum_j - log2(dt_j)
+    //   cf[j]   e^(r - cum_j) dt_j with r the cum at the last row of j's 32-column chunk: the column factor of the
+    //           chunks left of the diagonal, where e^(cum_i - cum_j) dt_j = e^(cum_i - r) * cf[j] and both
+    //           exponents are <= 0 for every row i below the chunk
+    // It runs up to two steps ahead of the element-wise warps (a table is rewritten once all 128 rows have
+    // released it), so the scan never sits on their critical path.
     const float a_log2 = A[h] * kLog2e;
-    {  // the state starts at zero
-      uint32_t z[32];
-#pragma unroll
-      for (int k = 0; k < 32; ++k) z[k] = 0u;
-      tmem_st32(tS + lane_addr, z);
-      tmem_st32(tS + lane_addr + 32, z);
-      tmem_wait_st();
-    }
     bool ok = true;
-    float dt_next[4];
-#pragma unroll
-    for (int e = 0; e < 4; ++e) dt_next[e] = dt_by_tma ? 0.f : dt[(static_cast<size_t>(b) * L + 4 * lane + e) * H + h];
-    // Prefix sum of dt*A over the 128 rows of step sp, every warp for itself (lane l holds rows 4l..4l+3);
-    // leaves total, cum_i and dt_i of this thread's row and this warp's copy of cum_j - log2(dt_j) in lb.
-    // Depends only on dt, so it runs for step s+1 while the last product of step s is in flight.
-    float total = 0.f, cum_i = 0.f, dt_i = 0.f;
-    float ref0 = 0.f, ref1 = 0.f, ref2 = 0.f;   // cum at the last row of column chunks 0..2 (32 columns each)
-    auto prefix = [&](int sp) -> bool {
+    for (int sp = 0; sp < nsteps && ok; ++sp) {
+      float *tab = pf_all + (sp & 1) * kPfFloats;
       float dt4[4], cum4[4];
       if (dt_by_tma) {
-        if (!__all_sync(0xffffffffu, mbar_wait(b_dt_full + 8 * (sp & 1), (sp >> 1) & 1, abort_flag))) return false;
+        ok = __all_sync(0xffffffffu, mbar_wait(b_dt_full + 8 * (sp & 1), (sp >> 1) & 1, abort_flag));
+        if (!ok) { if (lane == 0) ssd_report(status, kErrSsdPrefix, 2 * sp); break; }
         const float *tile = dt_tile + (sp & 1) * (kQ * 4) + (h & 3);
 #pragma unroll
         for (int e = 0; e < 4; ++e) dt4[e] = tile[(4 * lane + e) * 4];
       } else {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) dt4[e] = dt_next[e];
-      }
-      if (!dt_by_tma && sp + 1 < nsteps) {  // the dt of the step after, fetched a whole step ahead
-#pragma unroll
         for (int e = 0; e < 4; ++e)
-          dt_next[e] = ldg_pinned(dt + (static_cast<size_t>(b) * L + static_cast<size_t>(sp + 1) * kQ + 4 * lane + e) * H + h);
+          dt4[e] = dt[(static_cast<size_t>(b) * L + static_cast<size_t>(sp) * kQ + 4 * lane + e) * H + h];
       }
       cum4[0] = dt4[0] * a_log2;
 #pragma unroll
@@ -349,40 +338,44 @@ ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       const float excl = incl - cum4[3];
 #pragma unroll
       for (int e = 0; e < 4; ++e) cum4[e] += excl;
-      total = __shfl_sync(0xffffffffu, cum4[3], 31);
-      __syncwarp();  // this warp's readers of the previous step's lb (the decay pass) are done
       const float4 lbv =
           make_float4(cum4[0] - lg2(dt4[0]), cum4[1] - lg2(dt4[1]), cum4[2] - lg2(dt4[2]), cum4[3] - lg2(dt4[3]));
-      *reinterpret_cast<float4 *>(lb + 4 * lane) = lbv;
-      // Column factors for the chunks left of the diagonal: with r = cum at the last row of the 32-column chunk of j,
-      // e^(cum_i - cum_j) dt_j = e^(cum_i - r) * [e^(r - cum_j) dt_j] and both exponents are <= 0 for every row i
-      // below the chunk, so the decay of such a chunk is one factor per row and one per column instead of an
-      // exponential per element.
       const float r_own = __shfl_sync(0xffffffffu, cum4[3], lane | 7);
-      *reinterpret_cast<float4 *>(cf + 4 * lane) =
-          make_float4(ex2(r_own - lbv.x), ex2(r_own - lbv.y), ex2(r_own - lbv.z), ex2(r_own - lbv.w));
-      ref0 = __shfl_sync(0xffffffffu, cum4[3], 7);
-      ref1 = __shfl_sync(0xffffffffu, cum4[3], 15);
-      ref2 = __shfl_sync(0xffffffffu, cum4[3], 23);
-      __syncwarp();
-      // this thread's own row: lane (i mod 32) / 4 ... of this warp's block of 32 rows lives at lane 8*warp + lane/4
-      const int src = 8 * warp + (lane >> 2), comp = lane & 3;
-      cum_i = 0.f;
-      dt_i = 0.f;
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float cv = __shfl_sync(0xffffffffu, cum4[e], src), dv = __shfl_sync(0xffffffffu, dt4[e], src);
-        if (comp == e) { cum_i = cv; dt_i = dv; }
+      const float4 cfv = make_float4(ex2(r_own - lbv.x), ex2(r_own - lbv.y), ex2(r_own - lbv.z), ex2(r_own - lbv.w));
+      if (sp >= 2) {  // the table still holds step sp - 2 until every row has released it
+        ok = __all_sync(0xffffffffu, mbar_wait(b_pf_free + 8 * (sp & 1), ((sp >> 1) - 1) & 1, abort_flag));
+        if (!ok) { if (lane == 0) ssd_report(status, kErrSsdPrefix, 2 * sp + 1); break; }
       }
-      return true;
-    };
-    if (!prefix(0)) {
-      ssd_report(status, kErrSsdCompute, -1);
-      ok = false;
+      *reinterpret_cast<float4 *>(tab + 4 * lane) = make_float4(cum4[0], cum4[1], cum4[2], cum4[3]);
+      *reinterpret_cast<float4 *>(tab + kQ + 4 * lane) = make_float4(dt4[0], dt4[1], dt4[2], dt4[3]);
+      *reinterpret_cast<float4 *>(tab + 2 * kQ + 4 * lane) = lbv;
+      *reinterpret_cast<float4 *>(tab + 3 * kQ + 4 * lane) = cfv;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(b_pf_full + 8 * (sp & 1));
     }
+  } else {
+    // ================================ element-wise warps ==========================
+    const int i = warp * 32 + lane;                           // row of the step == TMEM lane
+    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    {  // the state starts at zero
+      uint32_t z[32];
+#pragma unroll
+      for (int k = 0; k < 32; ++k) z[k] = 0u;
+      tmem_st32(tS + lane_addr, z);
+      tmem_st32(tS + lane_addr + 32, z);
+      tmem_wait_st();
+    }
+    bool ok = true;
     for (int s = 0; s < nsteps && ok; ++s) {
       const uint32_t ph = s & 1;
       unsigned char *pX = pU + (s & 1) * kXBytes, *pXs = pU + ((s & 1) ^ 1) * kXBytes;
+      // this step's row quantities, from the prefix warp's table
+      ok = __all_sync(0xffffffffu, mbar_wait(b_pf_full + 8 * (s & 1), (s >> 1) & 1, abort_flag));
+      if (!ok) { ssd_report(status, kErrSsdCompute, 8 * s + 7); break; }
+      const float *tab = pf_all + (s & 1) * kPfFloats;
+      const float *lb = tab + 2 * kQ, *cf = tab + 3 * kQ;
+      const float cum_i = tab[i], dt_i = tab[kQ + i], total = tab[kQ - 1];
+      const float ref0 = tab[31], ref1 = tab[63], ref2 = tab[95];
 
       // ---- E1a: S_in -> 16 bit in smem; S *= e^cum_last.  (The state is final: the previous step's
       //      y_ready, waited for in E3, was committed after its state update.) ----
@@ -497,11 +490,7 @@ ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(b_m_ready);
-      if (s + 1 < nsteps && !prefix(s + 1)) {  // nothing of step s needs total, cum_i, dt_i or lb any more
-        ssd_report(status, kErrSsdCompute, 8 * s + 6);
-        ok = false;
-        break;
-      }
+      mbar_arrive(b_pf_free + 8 * (s & 1));   // nothing of step s reads the table any more
 
       // ---- E3: Y -> storage dtype -> the buffer x occupied (x is dead once Y is complete);
       //      the producer warp stores the tile with one TMA copy ----

@@ -27,8 +27,9 @@ SYMBOLS: dict[str, tuple] = {
     "nb200_status_read": (c_int, [c_void_p, c_void_p, c_void_p]),
     "nb200_decode_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "nb200_decode_splitk": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                                    c_int, c_int, c_float, c_void_p]),
-    "nb200_decode_paged_splitk": (c_int, [c_void_p] * 6 + [c_int] * 8 + [c_float, c_void_p]),
+                                    c_int, c_int, c_float, c_void_p, c_void_p]),
+    "nb200_decode_auto_splits": (c_int, [c_int, c_int, c_int, c_int]),
+    "nb200_decode_paged_splitk": (c_int, [c_void_p] * 6 + [c_int] * 9 + [c_float, c_void_p, c_void_p]),
     "nb200_decode_combine": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_int,
                                      c_void_p]),
     "nb200_decode_merge_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),

@@ -137,15 +137,20 @@ def _decl(name: str, args: list[tuple[str, str]], attrs: dict) -> str:
             "    return\n  }\n}\n")
 
 
-def decode_splitk_decl(name: str, B: int, Hq: int, Hkv: int, L: int, D: int, n_splits: int, dtype: str = "bf16") -> str:
-    """Declaration of split-K flash-decoding: (q, k, v, partials, out)."""
+def decode_splitk_decl(name: str, B: int, Hq: int, Hkv: int, L: int, D: int, n_splits: int, dtype: str = "bf16",
+                       auto_splits: bool = False) -> str:
+    """Declaration of split-K flash-decoding: (q, k, v, partials, out).
+
+    With ``auto_splits`` the partials memref is still sized for ``n_splits`` but the attribute says 0: the library
+    picks the count (at most ``n_splits``) that fills the GPU it runs on."""
+    attr_splits = 0 if auto_splits else n_splits
     return _decl(name, [
         ("q", f"memref<{B}x{Hq}x{D}x{dtype}>"),
         ("k", f"memref<{B}x{Hkv}x{L}x{D}x{dtype}>"),
         ("v", f"memref<{B}x{Hkv}x{L}x{D}x{dtype}>"),
         ("partials", f"memref<{B}x{Hq}x{n_splits}x{D + 2}xf32>"),
         ("out", f"memref<{B}x{Hq}x{D}x{dtype}>"),
-    ], {"htile.operator": "decode_splitk", "n_splits": n_splits, "scale": _f32(1.0 / math.sqrt(D))})
+    ], {"htile.operator": "decode_splitk", "n_splits": attr_splits, "scale": _f32(1.0 / math.sqrt(D))})
 
 
 def decode_paged_decl(name: str, B: int, Hq: int, Hkv: int, num_pages: int, max_pages: int, D: int, n_splits: int,

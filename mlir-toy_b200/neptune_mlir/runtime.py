@@ -86,18 +86,28 @@ def decode_workspace_floats(B, Hq, D, n_splits) -> int:
 
 
 def decode_splitk(q, k, v, partials, out, *, B, Hq, Hkv, L, D, n_splits, dtype, scale_log2) -> None:
-    """Split-K flash-decoding + LSE combine; ``partials`` is fp32 [B, Hq, n_splits, D + 2] scratch."""
+    """Split-K flash-decoding + LSE combine; ``partials`` is fp32 [B, Hq, n_splits, D + 2] scratch.
+
+    ``n_splits = 0`` lets the library choose the count for the GPU it runs on (nb200_decode_auto_splits), bounded
+    by the third extent of ``partials``, of which the first B*Hq*n*(D+2) floats are then used.
+    """
     _check("q", q, (B, Hq, D), dtype)
     _check("k", k, (B, Hkv, L, D), dtype)
     _check("v", v, (B, Hkv, L, D), dtype)
-    _check("partials", partials, (B, Hq, n_splits, D + 2), torch.float32)
+    cap = n_splits if n_splits > 0 else (partials.shape[2] if isinstance(partials, torch.Tensor) and partials.dim() == 4 else 0)
+    _check("partials", partials, (B, Hq, cap, D + 2), torch.float32)
     _check("out", out, (B, Hq, D), dtype)
     dev = _same_device(q, k, v, partials, out)
     lib = native.lib()
     with torch.cuda.device(dev):
         st = _stream(dev)
+        if n_splits == 0:
+            n_splits = lib.nb200_decode_auto_splits(B, Hkv, L, cap)
+            if n_splits <= 0:
+                raise native.NativeLibraryError("nb200_decode_auto_splits could not choose a split count")
         rc = lib.nb200_decode_splitk(q.data_ptr(), k.data_ptr(), v.data_ptr(), partials.data_ptr(), B, Hq, Hkv,
-                                     L, D, n_splits, native.DTYPE_CODES[dtype], float(scale_log2), st)
+                                     L, D, n_splits, native.DTYPE_CODES[dtype], float(scale_log2),
+                                     status_buffer(dev).data_ptr(), st)
         native.check(rc, "nb200_decode_splitk")
         rc = lib.nb200_decode_combine(partials.data_ptr(), out.data_ptr(), B * Hq, D, n_splits,
                                       n_splits * (D + 2), D + 2, native.DTYPE_CODES[dtype], st)
@@ -112,6 +122,8 @@ def decode_paged(q, k_pages, v_pages, block_table, seq_lens, partials, out, *, B
         if not (isinstance(pool, torch.Tensor) and pool.is_cuda and pool.is_contiguous() and pool.dim() == 4
                 and tuple(pool.shape[1:]) == (Hkv, page_size, D) and pool.dtype == _TORCH_DTYPES[dtype]):
             raise ValueError(f"{name}: expected a contiguous CUDA [num_pages, {Hkv}, {page_size}, {D}] {dtype} tensor")
+    if k_pages.shape[0] != v_pages.shape[0]:
+        raise ValueError("k_pages and v_pages must hold the same number of pages")
     _check("block_table", block_table, (B, max_pages), torch.int32)
     _check("seq_lens", seq_lens, (B,), torch.int32)
     _check("partials", partials, (B, Hq, n_splits, D + 2), torch.float32)
@@ -121,8 +133,9 @@ def decode_paged(q, k_pages, v_pages, block_table, seq_lens, partials, out, *, B
     with torch.cuda.device(dev):
         st = _stream(dev)
         rc = lib.nb200_decode_paged_splitk(q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
-                                           seq_lens.data_ptr(), partials.data_ptr(), B, Hq, Hkv, max_pages, page_size,
-                                           D, n_splits, native.DTYPE_CODES[dtype], float(scale_log2), st)
+                                           seq_lens.data_ptr(), partials.data_ptr(), B, Hq, Hkv, int(k_pages.shape[0]),
+                                           max_pages, page_size, D, n_splits, native.DTYPE_CODES[dtype],
+                                           float(scale_log2), status_buffer(dev).data_ptr(), st)
         native.check(rc, "nb200_decode_paged_splitk")
         rc = lib.nb200_decode_combine(partials.data_ptr(), out.data_ptr(), B * Hq, D, n_splits,
                                       n_splits * (D + 2), D + 2, native.DTYPE_CODES[dtype], st)

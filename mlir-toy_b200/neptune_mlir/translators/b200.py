@@ -194,8 +194,10 @@ class Translator:
             need(len(part) == 4 and part[:2] == (B, Hq) and part[3] == D + 2 and dts[3] == "f32",
                  "partials must be memref<BxHqxSx(D+2)xf32>")
             need(dts[0] in ("f16", "bf16") and dts[0] == dts[1] == dts[2] == dts[4], "q/k/v/out share f16 or bf16")
-            n_splits = part[2]
-            need(int(fn.attributes.get("n_splits", n_splits)) == n_splits, "n_splits attribute disagrees with partials")
+            # n_splits = 0 leaves the count to the library (it fills the GPU's CTA slots a whole number of times);
+            # the partials memref then only bounds it
+            n_splits = int(fn.attributes.get("n_splits", part[2]))
+            need(n_splits in (0, part[2]), "n_splits attribute disagrees with partials")
             scale = float(fn.attributes.get("scale", 1.0 / math.sqrt(D)))
             return self._runtime_call("decode_splitk", params, B=B, Hq=Hq, Hkv=Hkv, L=L, D=D, n_splits=n_splits,
                                       dtype=dts[0], scale_log2=scale * math.log2(math.e))

@@ -20,8 +20,14 @@ check, by the Python reader and pass -- wrapped in the stand-in's object model a
    interpreter on CPU tensors over their whole grid, and the outputs stored in
    ``reference_translations.npz`` with the SHA-256 of inputs and of the emitted source.
 
+3. The program of the reference's own shape as this build spells it (tests/data/attention_f16_1x32x4096x128.mlir,
+   non-causal f16 1x32x4096x128) is translated by all three reference translators and the emitted modules
+   are stored as text under ``reference_emitted/``.  They are outputs of the reference, kept so that the
+   benchmark can time the reference's GPU path (Triton / TileLang / cuTile JIT of what its translators emit)
+   beside this build's kernel on a machine that has no copy of the reference tree.
+
 Usage (needs the reference tree; run from the repository root):
-    python tests/golden/make_reference_translations.py /path/to/reference
+    python tests/golden/make_reference_translations.py /path/to/reference [--emit-only]
 """
 
 import ast
@@ -124,12 +130,33 @@ def run_source(source: str, name: str, grid, *tensors) -> None:
         getattr(mod, name)[grid](*tensors)
 
 
+EMITTED_PROGRAM = "attention_f16_1x32x4096x128"
+
+
+def emit_reference_modules(ref) -> None:
+    """What the three reference translators emit for this build's spelling of the reference-shape program."""
+    text = (ROOT / "tests" / "data" / f"{EMITTED_PROGRAM}.mlir").read_text()
+    out_dir = HERE / "reference_emitted"
+    out_dir.mkdir(exist_ok=True)
+    for name, mod in ref.items():
+        source = translate(mod, text, run_pass=(name != "tilelang"))
+        header = (f"# Emitted by the reference project's {name} translator (imported unmodified from the reference tree)\n"
+                  f"# for tests/data/{EMITTED_PROGRAM}.mlir; written by tests/golden/make_reference_translations.py.\n"
+                  "# Not product code: the benchmark launches it as the reference's own GPU path.\n")
+        (out_dir / f"{EMITTED_PROGRAM}_{name}.py").write_text(header + source + "\n")
+        print(f"wrote reference_emitted/{EMITTED_PROGRAM}_{name}.py ({len(source.splitlines())} lines)")
+
+
 def main() -> None:
-    if len(sys.argv) < 2 and "NEPTUNE_REFERENCE_ROOT" not in os.environ:
+    args = [a for a in sys.argv[1:] if not a.startswith("--")]
+    if not args and "NEPTUNE_REFERENCE_ROOT" not in os.environ:
         raise SystemExit(__doc__)
-    ref_root = Path(sys.argv[1] if len(sys.argv) > 1 else os.environ["NEPTUNE_REFERENCE_ROOT"])
+    ref_root = Path(args[0] if args else os.environ["NEPTUNE_REFERENCE_ROOT"])
     ref = load_reference_translator(ref_root)
     check_standin(ref, ref_root)
+    emit_reference_modules(ref)
+    if "--emit-only" in sys.argv:
+        return
     ref_triton = ref["triton"]
 
     store = {}

@@ -43,7 +43,7 @@ def main() -> int:
     lib = native.lib()
     st = torch.cuda.current_stream(dev).cuda_stream
     native.check(lib.nb200_decode_splitk(qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), part.data_ptr(), 1, Hq, Hkv, Ll,
-                                         D, splits, 1, scale_log2, st), "decode_splitk")
+                                         D, splits, 1, scale_log2, None, st), "decode_splitk")
     runtime.decode_combine(part, local, rows=Hq, D=D, n_splits=splits, row_stride=splits * (D + 2),
                            split_stride=D + 2, out_dtype="f32")
 

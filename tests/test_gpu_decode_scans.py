@@ -100,19 +100,25 @@ def test_decode_over_a_paged_cache_with_ragged_lengths(cuda, native_lib, Hq, Hkv
     lens = [1000, 0, 1, 63, 64, 65, 500]
     B, max_pages = len(lens), 16
     q, k, v = inputs.decode_inputs(B=B, Hq=Hq, Hkv=Hkv, L=max_pages * page, D=D, dtype=torch.bfloat16, config=41)
-    num_pages = B * max_pages + 5
+    used_pages = B * max_pages + 5
+    num_pages = used_pages + 1                          # one more page, which no sequence owns (see below)
     gen = torch.Generator().manual_seed(7)
-    perm = torch.randperm(num_pages, generator=gen)[:B * max_pages].view(B, max_pages).to(torch.int32)
+    perm = torch.randperm(used_pages, generator=gen)[:B * max_pages].view(B, max_pages).to(torch.int32)
     k_pool = torch.zeros((num_pages, Hkv, page, D), dtype=torch.bfloat16)
     v_pool = torch.zeros_like(k_pool)
     for b in range(B):
         for p in range(max_pages):
             k_pool[perm[b, p]] = k[b, :, p * page:(p + 1) * page]
             v_pool[perm[b, p]] = v[b, :, p * page:(p + 1) * page]
-    # entries past a sequence's last page must not be read: poison them
+    # entries past a sequence's last page must not be read: point them at a page of the pool that holds NaN, so
+    # that a stray read shows up as a wrong (non-finite) result rather than as an access outside the pool
+    sentinel = num_pages - 1
+    assert sentinel not in perm
+    k_pool[sentinel] = float("nan")
+    v_pool[sentinel] = float("nan")
     table = perm.clone()
     for b, n in enumerate(lens):
-        table[b, (n + page - 1) // page:] = 2 ** 30
+        table[b, (n + page - 1) // page:] = sentinel
     partials = torch.full((B, Hq, n_splits, D + 2), float("nan"), device=cuda)
     out = torch.full((B, Hq, D), float("nan"), dtype=torch.bfloat16, device=cuda)
     if n_splits == 3:  # once through an emitted module, the way the other operators are called
@@ -133,6 +139,61 @@ def test_decode_over_a_paged_cache_with_ragged_lengths(cuda, native_lib, Hq, Hkv
             continue
         ref = decode.decode_reference(q[b:b + 1], k[b:b + 1, :, :n], v[b:b + 1, :, :n])
         assert_storage_close(out[b:b + 1], ref, BF16_ATOL)
+
+
+def test_paged_decode_refuses_a_table_entry_outside_the_pool(cuda, native_lib):
+    """A block-table entry that is not a page of the pool is never dereferenced: the split that meets it yields
+    NaN, the status words name the entry, and the other sequences are computed as usual.  A length beyond what a
+    table row can address is cut to the row."""
+    from neptune_mlir import native, runtime
+
+    D, page, Hq, Hkv, n_splits = 128, 64, 8, 2, 2
+    B, max_pages = 3, 8
+    num_pages = B * max_pages
+    L = max_pages * page
+    q, k, v = inputs.decode_inputs(B=B, Hq=Hq, Hkv=Hkv, L=L, D=D, dtype=torch.bfloat16, config=42)
+    table = torch.arange(num_pages, dtype=torch.int32).view(B, max_pages)
+    k_pool = k.view(B, Hkv, max_pages, page, D).permute(0, 2, 1, 3, 4).reshape(num_pages, Hkv, page, D).contiguous()
+    v_pool = v.view(B, Hkv, max_pages, page, D).permute(0, 2, 1, 3, 4).reshape(num_pages, Hkv, page, D).contiguous()
+    lens = torch.tensor([L, L + 1000, L], dtype=torch.int32)          # sequence 1 claims more rows than its row holds
+    bad = table.clone()
+    bad[2, 5] = num_pages + 7                                         # sequence 2 has an entry outside the pool
+    partials = torch.full((B, Hq, n_splits, D + 2), float("nan"), device=cuda)
+    out = torch.full((B, Hq, D), float("nan"), dtype=torch.bfloat16, device=cuda)
+    finish()                                                          # status words clear before the call
+    runtime.decode_paged(q.to(cuda), k_pool.to(cuda), v_pool.to(cuda), bad.to(cuda), lens.to(cuda), partials, out,
+                         B=B, Hq=Hq, Hkv=Hkv, max_pages=max_pages, page_size=page, D=D, n_splits=n_splits, dtype="bf16",
+                         scale_log2=LOG2E / math.sqrt(D))
+    torch.cuda.synchronize()
+    with pytest.raises(ValueError, match=f"block table entry {num_pages + 7} is outside the page pool"):
+        runtime.check_status(cuda)
+    runtime.check_status(cuda)                                        # reading the status cleared it
+    assert bool(torch.isnan(out[2].float()).all())
+    for b in (0, 1):
+        ref = decode.decode_reference(q[b:b + 1], k[b:b + 1], v[b:b + 1])
+        assert_storage_close(out[b:b + 1], ref, BF16_ATOL)
+    assert native.lib().nb200_last_error() is not None
+
+
+def test_decode_auto_split_count(cuda, native_lib):
+    """n_splits = 0 in the declaration: the library picks the count for this GPU, bounded by the partials memref."""
+    from neptune_mlir import native, programs
+
+    B, Hq, Hkv, L, D, cap = 2, 8, 2, 8192, 128, 64
+    n = native.lib().nb200_decode_auto_splits(B, Hkv, L, cap)
+    assert 1 <= n <= cap and L // n >= 64
+    q, k, v = inputs.decode_inputs(B=B, Hq=Hq, Hkv=Hkv, L=L, D=D)
+    mod = translate_text(programs.decode_splitk_decl("dec_auto", B, Hq, Hkv, L, D, cap, auto_splits=True), "dec_auto")
+    partials = torch.full((B, Hq, cap, D + 2), float("nan"), device=cuda)
+    out = torch.full((B, Hq, D), float("nan"), dtype=torch.bfloat16, device=cuda)
+    mod.dec_auto(q.to(cuda), k.to(cuda), v.to(cuda), partials, out)
+    finish()
+    assert_storage_close(out, decode.decode_reference(q, k, v), BF16_ATOL)
+    # a whole number of waves where the problem is large enough to have a choice
+    sms = torch.cuda.get_device_properties(cuda).multi_processor_count
+    big = native.lib().nb200_decode_auto_splits(8, 8, 32768, 0)
+    waves = big * 64 / (2 * sms)
+    assert waves - int(waves) > 0.9 or waves == int(waves), (big, waves)
 
 
 def test_combine_with_gather_strides_and_partial_output(cuda, native_lib):

@@ -54,9 +54,9 @@ def test_version_and_argument_errors_without_a_gpu(native_lib):
     buf = ctypes.create_string_buffer(64)
     p = ctypes.addressof(buf)
     p += (-p) % 16
-    rc = lib.nb200_decode_splitk(p, p, p, p, 1, 8, 2, 1024, 64, 4, 1, 0.1, None)
+    rc = lib.nb200_decode_splitk(p, p, p, p, 1, 8, 2, 1024, 64, 4, 1, 0.1, None, None)
     assert rc == -2 and b"only 128" in lib.nb200_last_error()
-    rc = lib.nb200_decode_splitk(p, p, p, p, 1, 8, 3, 1024, 128, 4, 1, 0.1, None)
+    rc = lib.nb200_decode_splitk(p, p, p, p, 1, 8, 3, 1024, 128, 4, 1, 0.1, None, None)
     assert rc == -2
     rc = lib.nb200_selective_scan_fwd(p, p, p, p, p, p, p, p, 1, 64, 100, 16, 1, None)
     assert rc == -2 and b"multiple of 64" in lib.nb200_last_error()
@@ -88,12 +88,28 @@ def test_paged_decode_rejects_bad_calls_without_a_gpu(native_lib):
     buf = ctypes.create_string_buffer(64)
     p = ctypes.addressof(buf)
     p += (-p) % 16
-    rc = lib.nb200_decode_paged_splitk(p, p, p, p, p, p, 2, 8, 2, 16, 32, 128, 4, 1, 0.1, None)
+    rc = lib.nb200_decode_paged_splitk(p, p, p, p, p, p, 2, 8, 2, 40, 16, 32, 128, 4, 1, 0.1, None, None)
     assert rc == -2 and b"only 64 rows per page" in lib.nb200_last_error()
-    rc = lib.nb200_decode_paged_splitk(p, p, p, None, p, p, 2, 8, 2, 16, 64, 128, 4, 1, 0.1, None)
+    rc = lib.nb200_decode_paged_splitk(p, p, p, None, p, p, 2, 8, 2, 40, 16, 64, 128, 4, 1, 0.1, None, None)
     assert rc == -1
-    rc = lib.nb200_decode_paged_splitk(p, p, p, p, p, p, 2, 8, 3, 16, 64, 128, 4, 1, 0.1, None)
+    rc = lib.nb200_decode_paged_splitk(p, p, p, p, p, p, 2, 8, 3, 40, 16, 64, 128, 4, 1, 0.1, None, None)
     assert rc == -2
+
+
+def test_combine_and_static_decode_reject_a_misaligned_output_without_a_gpu(native_lib):
+    """16-bit outputs are written four elements (8 bytes) at a time: an output that starts at an odd element is
+    refused on the host instead of faulting on the device."""
+    lib = native.load(str(native_lib))
+    buf = ctypes.create_string_buffer(128)
+    p = ctypes.addressof(buf)
+    p += (-p) % 16
+    rc = lib.nb200_decode_combine(p, p + 2, 8, 128, 4, 4 * 130, 130, 1, None)
+    assert rc == -1 and b"out must be 8-byte aligned" in lib.nb200_last_error()
+    rc = lib.nb200_decode_combine(p, p + 2, 8, 128, 4, 4 * 130, 130, 2, None)
+    assert rc == -1 and b"out must be 4-byte aligned" in lib.nb200_last_error()
+    rc = lib.nb200_decode_fwd_static(p, p, p, p + 4, 1, 8, 2, 1024, 128, 4, 1, 0.1, None)
+    assert rc == -1 and b"out must be 8-byte aligned" in lib.nb200_last_error()
+    assert lib.nb200_decode_auto_splits(0, 8, 1024, 0) == 0
 
 
 def test_nccl_communicator_argument_checks():

@@ -12,7 +12,7 @@ import math
 import pytest
 import torch
 
-from oracle import inputs
+from oracle import decode, inputs
 
 pytestmark = pytest.mark.gpu
 
@@ -30,7 +30,7 @@ def _run_both(lib, cuda, B, Hq, Hkv, L, D, S, seed):
     partials = torch.empty((B, Hq, S, D + 2), device=cuda)
     want = torch.full((B, Hq, D), float("nan"), dtype=torch.bfloat16, device=cuda)
     native.check(lib.nb200_decode_splitk(q.data_ptr(), k.data_ptr(), v.data_ptr(), partials.data_ptr(), B, Hq, Hkv,
-                                         L, D, S, 1, scale_log2, st), "splitk")
+                                         L, D, S, 1, scale_log2, None, st), "splitk")
     native.check(lib.nb200_decode_combine(partials.data_ptr(), want.data_ptr(), B * Hq, D, S, S * (D + 2), D + 2, 1, st),
                  "combine")
     # allocation-free path: inputs and output only
@@ -38,7 +38,7 @@ def _run_both(lib, cuda, B, Hq, Hkv, L, D, S, seed):
     native.check(lib.nb200_decode_fwd_static(q.data_ptr(), k.data_ptr(), v.data_ptr(), got.data_ptr(), B, Hq, Hkv,
                                              L, D, S, 1, scale_log2, st), "decode_fwd_static")
     torch.cuda.synchronize()
-    return got, want
+    return got, want, decode.decode_reference(q.cpu(), k.cpu(), v.cpu())
 
 
 def test_static_scratch_decode_matches_workspace_decode_twice(cuda, native_lib):
@@ -47,11 +47,12 @@ def test_static_scratch_decode_matches_workspace_decode_twice(cuda, native_lib):
     lib = native.load(str(native_lib))
     # first call: larger problem; second call: smaller one, which finds the first call's partials still in the array
     for (B, Hq, Hkv, L, S), seed in (((4, 16, 4, 2048, 8), 0), ((2, 8, 2, 1024, 4), 7)):
-        got, want = _run_both(lib, cuda, B, Hq, Hkv, L, 128, S, seed)
+        got, want, oracle_out = _run_both(lib, cuda, B, Hq, Hkv, L, 128, S, seed)
         assert bool(torch.isfinite(got).all())
         err = (got.float() - want.float()).abs().max().item()
         assert err <= BF16_ATOL, f"max abs err {err}"
         assert torch.equal(got, want)  # same kernels, same order of operations
+        assert (got.float().cpu() - oracle_out).abs().max().item() <= BF16_ATOL   # and both agree with the CPU oracle
 
 
 def test_static_scratch_decode_rejects_oversized_problems(cuda, native_lib):
