@@ -465,7 +465,7 @@ def bench_extra(args, d: Dist, dev, flush, pk, pk_kind) -> dict:
         torch.cuda.empty_cache()
         if do_parity:
             from oracle import decode as odec, inputs
-            ns = 2
+            ns = 8
             qs, ks, vs = inputs.decode_inputs(B=ns, Hq=c["Hq"], Hkv=c["Hkv"], L=c["L"], D=c["D"])
             fn_s = load_callable(programs.decode_splitk_decl("decode_sample", ns, c["Hq"], c["Hkv"], c["L"], c["D"], c["S"]), "decode_sample")
             ps = torch.empty((ns, c["Hq"], c["S"], c["D"] + 2), device=dev)
@@ -611,7 +611,7 @@ def bench_extra(args, d: Dist, dev, flush, pk, pk_kind) -> dict:
         torch.cuda.empty_cache()
         if do_parity:
             from oracle import inputs, selective_scan as oscan
-            ns_d = 512
+            ns_d = 2048
             sargs = inputs.selective_scan_inputs(B=1, Dm=ns_d, L=c["L"], N=c["N"])
             fn_s = load_callable(programs.selective_scan_decl("scan_sample", 1, ns_d, c["L"], c["N"]), "scan_sample")
             os_ = torch.full((1, ns_d, c["L"]), float("nan"), dtype=bf, device=dev)
@@ -662,7 +662,7 @@ def bench_extra(args, d: Dist, dev, flush, pk, pk_kind) -> dict:
         torch.cuda.empty_cache()
         if do_parity:
             from oracle import inputs, ssd as ossd
-            hs = 8
+            hs = 16
             sargs = inputs.ssd_inputs(B=1, L=c["L"], H=hs, P=c["P"], N=c["N"], G=c["G"])
             wsb = runtime.ssd_workspace_bytes(1, c["L"], hs, c["P"], c["N"], c["G"], c["chunk"])
             fn_s = load_callable(programs.ssd_chunk_scan_decl("ssd_sample", 1, c["L"], hs, c["P"], c["N"], c["G"], c["chunk"], wsb), "ssd_sample")
@@ -820,7 +820,7 @@ def main() -> None:
     cpu = None
     if d.rank == 0 and not args.skip_cpu and d.world == 1:
         torch.set_num_threads(os.cpu_count() or 1)
-        heads = 64
+        heads = 128
         cpu_attention_sample(2)  # warm the thread pool
         secs, tf = cpu_attention_sample(heads)
         cpu = {"value": tf, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port", "seconds": secs,

@@ -649,7 +649,7 @@ decode_combine_kernel(const float *__restrict__ partials, void *__restrict__ out
       dst[kHeadDim + 1] = lsum;
     }
   } else {
-    const float inv = lsum > 0.f ? 1.f / lsum : 0.f;   // a sequence of length 0 (paged cache) yields zeros
+    const float inv = lsum == 0.f ? 0.f : 1.f / lsum;  // a sequence of length 0 (paged cache) yields zeros; a NaN-poisoned partial stays NaN
     uint2 w;
     w.x = pack2<ODT>(acc.x * inv, acc.y * inv);
     w.y = pack2<ODT>(acc.z * inv, acc.w * inv);
