@@ -204,14 +204,22 @@ int nb200_selective_scan_fwd(const void *u, const void *delta, const float *A, c
  * Mamba-2 SSD chunked scan forward (no counterpart in the reference).
  *   x, y : [B, L, H, P]   dt : fp32 [B, L, H] (already soft-plused)   A : fp32 [H]
  *   Bm, Cm : [B, L, G, N]  (head h reads group h / (H / G))
- *   workspace : nb200_ssd_workspace_bytes(...) bytes of device memory.  The recurrent state stays on
- *               chip, so this is only a status buffer (NB200_STATUS_WORDS int32) that the call clears
- *               and in which an expired device-side wait is recorded; read it with nb200_status_read.
+ *   workspace : nb200_ssd_workspace_bytes(...) bytes of device memory, 16-byte aligned.  It starts with a status
+ *               buffer (NB200_STATUS_WORDS int32) that the call clears and in which an expired device-side wait
+ *               is recorded; read it with nb200_status_read.  The recurrent state itself stays on chip.  The
+ *               rest is used only when the call cuts the sequences into segments so that a problem with few
+ *               (batch, head) pairs still fills the GPU: the fp32 state entering each later segment is prepared
+ *               there by two small kernels before the main one (three launches instead of one;
+ *               nb200_ssd_launches tells which).  The size does not depend on the device.
  * P == 64, N == 128, chunk in {64, 128, 256}, L a multiple of 128 and of chunk.  The kernel walks the
  * sequence in steps of 128 rows whatever `chunk` says; the result does not depend on the chunk length
- * beyond rounding.
+ * beyond rounding.  A CTA evaluates two heads that share B and C (H / G even), otherwise one.
  */
 size_t nb200_ssd_workspace_bytes(int B, int L, int H, int P, int N, int G, int chunk);
+
+/* Kernel launches that nb200_ssd_chunk_scan_fwd makes for this problem on the current device: 1, or 3 when the
+ * sequences are cut into segments.  0 for an unsupported shape. */
+int nb200_ssd_launches(int B, int L, int H, int P, int N, int G, int chunk);
 
 int nb200_ssd_chunk_scan_fwd(const void *x, const float *dt, const float *A, const void *Bm,
                              const void *Cm, void *y, void *workspace,

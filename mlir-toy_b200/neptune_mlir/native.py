@@ -39,6 +39,7 @@ SYMBOLS: dict[str, tuple] = {
                                         c_int, c_int, c_float, c_void_p]),
     "nb200_selective_scan_fwd": (c_int, [c_void_p] * 8 + [c_int] * 5 + [c_void_p]),
     "nb200_ssd_workspace_bytes": (c_size_t, [c_int] * 7),
+    "nb200_ssd_launches": (c_int, [c_int] * 7),
     "nb200_ssd_chunk_scan_fwd": (c_int, [c_void_p] * 7 + [c_int] * 8 + [c_void_p]),
 }
 

@@ -204,6 +204,11 @@ def ssd_workspace_bytes(B, L, H, P, N, G, chunk) -> int:
     return native.lib().nb200_ssd_workspace_bytes(B, L, H, P, N, G, chunk)
 
 
+def ssd_launches(B, L, H, P, N, G, chunk) -> int:
+    """Kernel launches one SSD call makes on the current device (3 when the sequences are cut into segments)."""
+    return native.lib().nb200_ssd_launches(B, L, H, P, N, G, chunk)
+
+
 def ssd_chunk_scan(x, dt, A, Bm, Cm, workspace, y, *, B, L, H, P, N, G, chunk, dtype) -> None:
     """Mamba-2 SSD chunked scan forward; ``workspace`` is a uint8 tensor of ssd_workspace_bytes(...)."""
     _check("x", x, (B, L, H, P), dtype)

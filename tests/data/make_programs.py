@@ -22,8 +22,11 @@ from neptune_mlir.translators import b200  # noqa: E402
 DATA = Path(__file__).resolve().parent
 GOLDEN = ROOT / "tests" / "golden"
 
-# workspace of the SSD configuration: the status words only (see include/nb200.h)
-SSD_WS = 16
+from neptune_mlir import native  # noqa: E402
+
+# workspace of the SSD configuration, as the library sizes it (status words plus room for the states that are
+# handed from segment to segment when a sequence is cut; see include/nb200.h)
+SSD_WS = native.lib().nb200_ssd_workspace_bytes(4, 8192, 64, 64, 128, 1, 256)
 
 PROGRAMS = {
     "attention_f16_1x32x4096x128": programs.attention_htile("attention_f16", 1, 32, 4096, 128, "f16", causal=False),

@@ -334,6 +334,36 @@ def test_ssd_head_count_not_a_multiple_of_four(cuda, native_lib):
     assert_rms_close(y, ref, 2.0 ** -8)
 
 
+@pytest.mark.parametrize("segments,H,G", [(2, 4, 1), (3, 4, 2), (8, 4, 1), (4, 3, 1), (2, 6, 2)])
+def test_ssd_sequences_cut_into_segments(cuda, native_lib, monkeypatch, segments, H, G):
+    """A sequence cut into segments that run as separate CTAs: the state entering each later segment comes from
+    the segment-state and chain kernels.  NB200_SSD_SEGMENTS forces the cut that the library would only choose
+    for a problem with few (batch, head) pairs.  Head counts 3 and 6 with 2 groups run one head per CTA (no pair
+    shares B and C); 8 segments of a 1024-row sequence are one step each."""
+    from neptune_mlir import runtime
+
+    B, L, P, N, chunk = 2, 1024, 64, 128, 128
+    args = inputs.ssd_inputs(B=B, L=L, H=H, P=P, N=N, G=G, config=52)
+    dev_args = [a.to(cuda) for a in args]
+    ws = torch.empty(runtime.ssd_workspace_bytes(B, L, H, P, N, G, chunk), dtype=torch.uint8, device=cuda)
+    outs = {}
+    for k in (1, segments):
+        monkeypatch.setenv("NB200_SSD_SEGMENTS", str(k))
+        assert runtime.ssd_launches(B, L, H, P, N, G, chunk) == (1 if k == 1 else 3)
+        y = torch.full((B, L, H, P), float("nan"), dtype=torch.bfloat16, device=cuda)
+        runtime.ssd_chunk_scan(*dev_args, ws, y, B=B, L=L, H=H, P=P, N=N, G=G, chunk=chunk, dtype="bf16")
+        finish()
+        runtime.check_workspace_status(ws)
+        outs[k] = y
+    ref = ssd.ssd_reference(*args)
+    for k, y in outs.items():
+        assert_storage_close(y, ref, BF16_ATOL, 2 * BF16_ULP, scale_by_rms=True)
+        assert_rms_close(y, ref, 2.0 ** -8)
+    # the first segment is computed exactly as in the uncut run
+    rows = (L // 128 + segments - 1) // segments * 128
+    assert torch.equal(outs[1][:, :rows], outs[segments][:, :rows])
+
+
 def test_ssd_config5_full_size_sampled(cuda, native_lib):
     """B=4, L=8192, H=64, P=64, N=128, chunk 256; heads are independent, a sample is checked in full."""
     from neptune_mlir import runtime

@@ -123,7 +123,11 @@ def test_nccl_communicator_argument_checks():
 def test_workspace_sizes(native_lib):
     lib = native.load(str(native_lib))
     assert lib.nb200_decode_workspace_bytes(64, 32, 128, 16) == 64 * 32 * 16 * 130 * 4
-    assert lib.nb200_ssd_workspace_bytes(4, 8192, 64, 64, 128, 1, 256) == 16
+    # status words (padded to 256) + at most 512 CTAs' worth of segments: 4 per sequence here, 3 hand-over slots
+    # of one total (fp32) and one 128 x 64 fp32 state per (batch, head)
+    slots = 4 * 64 * 3
+    assert lib.nb200_ssd_workspace_bytes(4, 8192, 64, 64, 128, 1, 256) == 256 + slots * 4 + slots * 8192 * 4
+    assert lib.nb200_ssd_workspace_bytes(64, 8192, 64, 64, 128, 1, 256) == 256     # enough chains: never cut
     assert lib.nb200_ssd_workspace_bytes(4, 8192, 64, 32, 128, 1, 256) == 0
 
 
