@@ -209,7 +209,7 @@ int nb200_selective_scan_fwd(const void *u, const void *delta, const float *A, c
  *               is recorded; read it with nb200_status_read.  The recurrent state itself stays on chip.  The
  *               rest is used only when the call cuts the sequences into segments so that a problem with few
  *               (batch, head) pairs still fills the GPU: the fp32 state entering each later segment is prepared
- *               there by two small kernels before the main one (three launches instead of one;
+ *               there by one more kernel before the main one (two launches instead of one;
  *               nb200_ssd_launches tells which).  The size does not depend on the device.
  * P == 64, N == 128, chunk in {64, 128, 256}, L a multiple of 128 and of chunk.  The kernel walks the
  * sequence in steps of 128 rows whatever `chunk` says; the result does not depend on the chunk length
@@ -217,7 +217,7 @@ int nb200_selective_scan_fwd(const void *u, const void *delta, const float *A, c
  */
 size_t nb200_ssd_workspace_bytes(int B, int L, int H, int P, int N, int G, int chunk);
 
-/* Kernel launches that nb200_ssd_chunk_scan_fwd makes for this problem on the current device: 1, or 3 when the
+/* Kernel launches that nb200_ssd_chunk_scan_fwd makes for this problem on the current device: 1, or 2 when the
  * sequences are cut into segments.  0 for an unsupported shape. */
 int nb200_ssd_launches(int B, int L, int H, int P, int N, int G, int chunk);
 

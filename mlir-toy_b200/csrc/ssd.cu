@@ -31,10 +31,10 @@
 // flight, so that no element-wise pass waits for a buffer: 208 KB.  Tensor memory (all 512 columns):
 // G 0-127; per head the masked 16-bit product 64, Y 64 and the state 64 columns.
 //
-// A sequence can be cut into segments that run as separate CTAs: segment k > 0 starts from a state that
-// ssd_segment_state_kernel (the state each earlier segment would reach from zero) and ssd_chain_kernel (the
-// recurrence over those) prepared in global memory.  That is how a problem with few (batch, head) pairs, e.g.
-// one GPU's share of the heads, still fills the SMs.
+// A sequence can be cut into segments that run as separate CTAs: ssd_segment_state_kernel first leaves in global
+// memory the state each segment but the last would reach from zero and its total decay; a CTA of segment k > 0
+// then starts from the recurrence over the earlier segments' states.  That is how a problem with few
+// (batch, head) pairs, e.g. one GPU's share of the heads, still fills the SMs.
 //
 // All exponents are <= 0 (A < 0), so nothing overflows.  Every barrier exists twice and alternates with the
 // step, so a waiter can never be lapped; every wait is bounded and reports through the status words.
@@ -114,7 +114,7 @@ ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
                  const __grid_constant__ CUtensorMap tm_c, const __grid_constant__ CUtensorMap tm_y,
                  const __grid_constant__ CUtensorMap tm_dt, int dt_by_tma, const float *__restrict__ dt,
                  const float *__restrict__ A, int L, int H, int G, int lanes, int nseg, int steps_per_seg,
-                 const float *__restrict__ seg_states, int *status) {
+                 const float *__restrict__ seg_states, const float *__restrict__ seg_totals, int *status) {
   extern __shared__ __align__(1024) unsigned char smem[];
   const uint32_t base = smem_u32(smem);
   if ((base & 1023u) != 0) {
@@ -401,23 +401,33 @@ ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
     const int wq = warp & 3;                                   // TMEM lane quarter of this warp
     const int i = wq * 32 + lane;                              // row of the step == TMEM lane
     const uint32_t lane_addr = static_cast<uint32_t>(wq * 32) << 16;
-    {  // the incoming state: zero for the first segment, else what the chain over the earlier segments left
-      uint32_t z[kP];
+    {  // the incoming state: zero for the first segment; else the recurrence over the states Z_j that the earlier
+       // segments reach from zero, S_in = sum_j 2^(T_{j+1} + ... + T_{seg-1}) Z_j (T_j: total log2 decay of segment
+       // j), summed from the nearest segment backwards until the weight underflows
+      float acc[kP];
+#pragma unroll
+      for (int k = 0; k < kP; ++k) acc[k] = 0.f;
       if (seg > 0) {
-        const float4 *src = reinterpret_cast<const float4 *>(
-            seg_states + ((static_cast<size_t>(b) * H + h) * (nseg - 1) + (seg - 1)) * kStateFloats + static_cast<size_t>(i) * kP);
+        const size_t slot0 = (static_cast<size_t>(b) * H + h) * (nseg - 1);
+        float lg = 0.f;
+        for (int j = seg - 1; j >= 0; --j) {
+          const float wgt = ex2(lg);
+          if (wgt == 0.f) break;   // the same for every thread of the CTA's head
+          const float4 *src = reinterpret_cast<const float4 *>(seg_states + (slot0 + j) * kStateFloats + static_cast<size_t>(i) * kP);
 #pragma unroll
-        for (int k = 0; k < kP / 4; ++k) {
-          const float4 v = src[k];
-          z[4 * k] = __float_as_uint(v.x);
-          z[4 * k + 1] = __float_as_uint(v.y);
-          z[4 * k + 2] = __float_as_uint(v.z);
-          z[4 * k + 3] = __float_as_uint(v.w);
+          for (int k = 0; k < kP / 4; ++k) {
+            const float4 v = src[k];
+            acc[4 * k] = fmaf(wgt, v.x, acc[4 * k]);
+            acc[4 * k + 1] = fmaf(wgt, v.y, acc[4 * k + 1]);
+            acc[4 * k + 2] = fmaf(wgt, v.z, acc[4 * k + 2]);
+            acc[4 * k + 3] = fmaf(wgt, v.w, acc[4 * k + 3]);
+          }
+          lg += seg_totals[slot0 + j];
         }
-      } else {
-#pragma unroll
-        for (int k = 0; k < kP; ++k) z[k] = 0u;
       }
+      uint32_t z[kP];
+#pragma unroll
+      for (int k = 0; k < kP; ++k) z[k] = __float_as_uint(acc[k]);
       tmem_st32(tS + lane_addr, *reinterpret_cast<uint32_t(*)[32]>(z));
       tmem_st32(tS + lane_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(z + 32));
       tmem_wait_st();
@@ -582,30 +592,31 @@ ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
 // ---- the state a segment reaches from zero ------------------------------------------------------------
 // Z = sum_j e^(cum_end - cum_j) dt_j x_j (outer) B_j over the rows of one segment of one (batch, head), and the
 // segment's total log2 decay cum_end.  Weights are taken relative to the END of the segment, so the accumulator
-// needs no rescaling between steps: one tensor-core product per 128 rows into the same TMEM columns.  The
-// exponent of row j of step s is (total of step s - cum_j inside the step) + (sum of the totals of the later
-// steps), both summed from small terms, so that it is accurate where it matters: near the end of the segment.
-// Warps 0-3: thread i = row i: w_i x_i in place in shared memory; warp 4: TMA producer (x, B, dt; two stages);
-// warp 5: MMA issuer.
-constexpr int kSegStages = 2;
-constexpr int kSegThreads = 192;
-constexpr int kSegStageBytes = kBCBytes + kXBytes + kDtBytes;
-constexpr int kSegSmem = kSegStages * kSegStageBytes + 2048;
+// needs no rescaling between steps: one tensor-core product per 128 rows into the same TMEM columns.  The steps
+// are taken from the LAST one of the segment backwards, so that the decay from the end of a step to the end of
+// the segment is simply the running sum of the totals of the steps already done; the exponent of row j is
+// (total of its step - cum_j inside the step) + that sum, both summed from small terms, which keeps it accurate
+// where it matters: near the end of the segment.
+// Like the fused kernel a CTA takes two heads that share B (one head if they do not): warps 0-3 / 4-7: thread i =
+// row i of head 0 / 1: w_i x_i in place in shared memory; warp 8: TMA producer (B, x, dt; three stages, so that
+// loads run two steps ahead of the arithmetic); warp 9: MMA issuer.
+constexpr int kSegStages = 3;
+constexpr int kSegThreads = 320;
+constexpr int kSegStageBytes = kBCBytes + 2 * kXBytes + 2 * kDtBytes;   // 68 KB
+constexpr int kSegSmem = kSegStages * kSegStageBytes + 1024;
 
-constexpr int kSegMaxSteps = 448;   // steps of one segment whose totals fit the table below
 struct SegBarriers {
   uint64_t full[kSegStages], ready[kSegStages], empty[kSegStages], done;
   uint32_t tmem_base;
   int abort_flag;
-  float suffix[kSegMaxSteps];   // sum of dt over the steps after step s (then times A log2 e: the decay from the end of step s to the end of the segment)
 };
-static_assert(sizeof(SegBarriers) <= 2048, "segment barrier block");
+static_assert(sizeof(SegBarriers) <= 1024, "segment barrier block");
 
 template <int DT>
-__global__ void __launch_bounds__(kSegThreads, 2)
+__global__ void __launch_bounds__(kSegThreads, 1)
 ssd_segment_state_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_b,
                          const __grid_constant__ CUtensorMap tm_dt, int dt_by_tma, const float *__restrict__ dt,
-                         const float *__restrict__ A, int L, int H, int G, int nseg, int steps_per_seg,
+                         const float *__restrict__ A, int L, int H, int G, int lanes, int nseg, int steps_per_seg,
                          float *__restrict__ seg_states, float *__restrict__ seg_totals, int *status) {
   extern __shared__ __align__(1024) unsigned char smem[];
   const uint32_t base = smem_u32(smem);
@@ -616,9 +627,10 @@ ssd_segment_state_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
   SegBarriers *bars = reinterpret_cast<SegBarriers *>(smem + kSegStages * kSegStageBytes);
   volatile int *abort_flag = &bars->abort_flag;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int nsm1 = nseg - 1;
-  const int seg = blockIdx.x % nsm1, h = (blockIdx.x / nsm1) % H, b = blockIdx.x / (nsm1 * H);
-  const int g = h / (H / G);
+  const int nsm1 = nseg - 1, groups = H / lanes;
+  const int seg = blockIdx.x % nsm1, hg = (blockIdx.x / nsm1) % groups, b = blockIdx.x / (nsm1 * groups);
+  const int h_first = hg * lanes;
+  const int g = h_first / (H / G);
   const int s_begin = seg * steps_per_seg, nsteps = steps_per_seg;   // every segment but the last is full
   const size_t row0 = static_cast<size_t>(b) * L + static_cast<size_t>(s_begin) * kQ;
 
@@ -626,7 +638,7 @@ ssd_segment_state_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
     bars->abort_flag = 0;
     for (int p = 0; p < kSegStages; ++p) {
       mbar_init(smem_u32(&bars->full[p]), 1);
-      mbar_init(smem_u32(&bars->ready[p]), 128);
+      mbar_init(smem_u32(&bars->ready[p]), 128 * lanes);
       mbar_init(smem_u32(&bars->empty[p]), 1);
     }
     mbar_init(smem_u32(&bars->done), 1);
@@ -634,17 +646,16 @@ ssd_segment_state_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
     fence_proxy_async_smem();
   }
   __syncthreads();
-  if (warp == 5) {
-    tmem_alloc(smem_u32(&bars->tmem_base), 64);
+  if (warp == 9) {
+    tmem_alloc(smem_u32(&bars->tmem_base), 128);
     tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tZ = bars->tmem_base;
-  const float a_log2 = A[h] * kLog2e;
 
-  if (warp == 4) {
+  if (warp == 8) {
     if (lane == 0) {
       bool ok = true;
       int issued = 0;
@@ -655,12 +666,14 @@ ssd_segment_state_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
           if (!ok) { ssd_report(status, kErrSegState, 4 * s); break; }
         }
         const uint32_t sb = base + st * kSegStageBytes, bar = smem_u32(&bars->full[st]);
-        const int row = static_cast<int>(row0) + s * kQ;
-        mbar_arrive_expect_tx(bar, kBCBytes + kXBytes + (dt_by_tma ? kDtBytes : 0));
+        const int row = static_cast<int>(row0) + (nsteps - 1 - s) * kQ;   // last step of the segment first
+        mbar_arrive_expect_tx(bar, kBCBytes + lanes * (kXBytes + (dt_by_tma ? kDtBytes : 0)));
         tma_load_2d(sb, &tm_b, g * kN, row, bar);
         tma_load_2d(sb + kBCBox, &tm_b, g * kN + 64, row, bar);
-        tma_load_2d(sb + kBCBytes, &tm_x, h * kP, row, bar);
-        if (dt_by_tma) tma_load_2d(sb + kBCBytes + kXBytes, &tm_dt, h & ~3, row, bar);
+        for (int q = 0; q < lanes; ++q) {
+          tma_load_2d(sb + kBCBytes + q * kXBytes, &tm_x, (h_first + q) * kP, row, bar);
+          if (dt_by_tma) tma_load_2d(sb + kBCBytes + 2 * kXBytes + q * kDtBytes, &tm_dt, (h_first + q) & ~3, row, bar);
+        }
         ++issued;
       }
       if (!ok) {
@@ -676,7 +689,7 @@ ssd_segment_state_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
       }
     }
     __syncwarp();
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     if (lane == 0) {
       constexpr int fmt = (DT == NB200_BF16) ? 1 : 0;
       constexpr uint32_t id_z = umma_idesc_f16_ab(fmt, 1, 1, kN, kP);
@@ -687,52 +700,38 @@ ssd_segment_state_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
         if (!ok) { ssd_report(status, kErrSegState, 4 * s + 1); break; }
         tc_fence_after();
         const uint32_t sb = base + st * kSegStageBytes;
-        const uint64_t dBt0 = umma_desc_sw128(sb, kBCBox, 1024), dX0 = umma_desc_sw128(sb + kBCBytes, kXBytes, 1024);
+        const uint64_t dBt0 = umma_desc_sw128(sb, kBCBox, 1024);
+        for (int q = 0; q < lanes; ++q) {
+          const uint64_t dX0 = umma_desc_sw128(sb + kBCBytes + q * kXBytes, kXBytes, 1024);
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          umma_ss(tZ, dBt0 + static_cast<uint64_t>((kk * 2048) >> 4), dX0 + static_cast<uint64_t>((kk * 2048) >> 4), id_z,
-                  (s > 0 || kk > 0) ? 1u : 0u);
+          for (int kk = 0; kk < 8; ++kk)
+            umma_ss(tZ + 64 * q, dBt0 + static_cast<uint64_t>((kk * 2048) >> 4), dX0 + static_cast<uint64_t>((kk * 2048) >> 4),
+                    id_z, (s > 0 || kk > 0) ? 1u : 0u);
+        }
         umma_commit(smem_u32(&bars->empty[st]));
       }
       if (ok) umma_commit(smem_u32(&bars->done));
     }
     __syncwarp();
-  } else {
-    const int i = warp * 32 + lane;
-    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
-    // sums of dt per step (warp w takes steps w, w + 4, ...), then their suffix sums
-    for (int s = warp; s < nsteps; s += 4) {
-      float part = 0.f;
-#pragma unroll
-      for (int e = 0; e < 4; ++e) part += dt[(row0 + static_cast<size_t>(s) * kQ + 4 * lane + e) * H + h];
-#pragma unroll
-      for (int d = 16; d >= 1; d >>= 1) part += __shfl_xor_sync(0xffffffffu, part, d);
-      if (lane == 0) bars->suffix[s] = part;
-    }
-    asm volatile("bar.sync 1, 128;" ::: "memory");
-    float seg_total = 0.f;
-    if (i == 0) {
-      float run = 0.f;
-      for (int s = nsteps - 1; s >= 0; --s) {
-        const float t = bars->suffix[s];
-        bars->suffix[s] = run * a_log2;
-        run += t;
-      }
-      seg_total = run * a_log2;
-    }
-    asm volatile("bar.sync 1, 128;" ::: "memory");
+  } else if ((warp >> 2) < lanes) {
+    const int q = warp >> 2, wq = warp & 3, h = h_first + q;
+    const int i = wq * 32 + lane;
+    const uint32_t lane_addr = static_cast<uint32_t>(wq * 32) << 16;
+    const float a_log2 = A[h] * kLog2e;
+    float after = 0.f;   // log2 decay from the end of the step in hand to the end of the segment
     bool ok = true;
     for (int s = 0; s < nsteps && ok; ++s) {
       const int st = s % kSegStages;
       ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars->full[st]), (s / kSegStages) & 1, abort_flag));
       if (!ok) { ssd_report(status, kErrSegState, 4 * s + 2); break; }
-      unsigned char *pX = smem + st * kSegStageBytes + kBCBytes;
-      const float *dtt = reinterpret_cast<const float *>(smem + st * kSegStageBytes + kBCBytes + kXBytes);
+      unsigned char *pX = smem + st * kSegStageBytes + kBCBytes + q * kXBytes;
+      const float *dtt = reinterpret_cast<const float *>(smem + st * kSegStageBytes + kBCBytes + 2 * kXBytes + q * kDtBytes);
       // every warp scans the 128 dt values of the step itself (lane l: rows 4l..4l+3), then picks its own row's
       float dt4[4], cum4[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e)
-        dt4[e] = dt_by_tma ? dtt[(4 * lane + e) * 4 + (h & 3)] : dt[(row0 + static_cast<size_t>(s) * kQ + 4 * lane + e) * H + h];
+        dt4[e] = dt_by_tma ? dtt[(4 * lane + e) * 4 + (h & 3)]
+                           : dt[(row0 + static_cast<size_t>(nsteps - 1 - s) * kQ + 4 * lane + e) * H + h];
       cum4[0] = dt4[0] * a_log2;
 #pragma unroll
       for (int e = 1; e < 4; ++e) cum4[e] = cum4[e - 1] + dt4[e] * a_log2;
@@ -744,14 +743,15 @@ ssd_segment_state_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
       }
       const float excl = incl - cum4[3];
       const float step_total = __shfl_sync(0xffffffffu, incl, 31);
-      const int src = 8 * warp + (lane >> 2), comp = lane & 3;
+      const int src = 8 * wq + (lane >> 2), comp = lane & 3;
       float cum_i = 0.f, dt_i = 0.f;
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const float cv = __shfl_sync(0xffffffffu, cum4[e] + excl, src), dv = __shfl_sync(0xffffffffu, dt4[e], src);
         if (comp == e) { cum_i = cv; dt_i = dv; }
       }
-      const float wi = ex2((step_total - cum_i) + bars->suffix[s]) * dt_i;
+      const float wi = ex2((step_total - cum_i) + after) * dt_i;
+      after += step_total;
 #pragma unroll
       for (int cc = 0; cc < 8; ++cc) {
         uint4 *p = reinterpret_cast<uint4 *>(pX + sw128(i, cc));
@@ -770,8 +770,8 @@ ssd_segment_state_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
     if (ok) {
       tc_fence_after();
       uint32_t zv[kP];
-      tmem_ld32p(tZ + lane_addr, zv);
-      tmem_ld32p(tZ + lane_addr + 32, zv + 32);
+      tmem_ld32p(tZ + 64 * q + lane_addr, zv);
+      tmem_ld32p(tZ + 64 * q + lane_addr + 32, zv + 32);
       tmem_wait_ld();
       const size_t slot = (static_cast<size_t>(b) * H + h) * nsm1 + seg;
       float4 *dst = reinterpret_cast<float4 *>(seg_states + slot * kStateFloats + static_cast<size_t>(i) * kP);
@@ -779,28 +779,14 @@ ssd_segment_state_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
       for (int k = 0; k < kP / 4; ++k)
         dst[k] = make_float4(__uint_as_float(zv[4 * k]), __uint_as_float(zv[4 * k + 1]), __uint_as_float(zv[4 * k + 2]),
                              __uint_as_float(zv[4 * k + 3]));
-      if (i == 0) seg_totals[slot] = seg_total;
+      if (i == 0) seg_totals[slot] = after;
     }
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 9) {
     tc_fence_after();
-    tmem_dealloc(tZ, 64);
-  }
-}
-
-// S_in(k+1) = 2^total_k S_in(k) + Z_k over the segments of one (batch, head), in place: slot k holds Z_k on
-// entry and the state entering segment k + 1 on exit.
-__global__ void ssd_chain_kernel(float *__restrict__ seg_states, const float *__restrict__ seg_totals, int nsm1) {
-  const size_t bh = blockIdx.y;
-  const int e = blockIdx.x * blockDim.x + threadIdx.x;
-  if (e >= kStateFloats) return;
-  float acc = 0.f;
-  for (int k = 0; k < nsm1; ++k) {
-    float *p = seg_states + (bh * nsm1 + k) * kStateFloats + e;
-    acc = ex2(seg_totals[bh * nsm1 + k]) * acc + *p;
-    *p = acc;
+    tmem_dealloc(tZ, 128);
   }
 }
 
@@ -837,8 +823,8 @@ SsdPlan ssd_plan(int B, int L, int H, int G, int sms) {
     const double waves = static_cast<double>((ctas + sms - 1) / sms);
     double cost = waves * (sps + 1.0);
     if (k > 1) {
-      const long long ctas_a = (long long)B * H * (k - 1);
-      cost += static_cast<double>((ctas_a + 2 * sms - 1) / (2 * sms)) * (0.4 * sps + 0.5) + 2.0;
+      const long long ctas_a = chains * (k - 1);
+      cost += static_cast<double>((ctas_a + sms - 1) / sms) * (0.25 * sps + 1.0) + 1.0;
     }
     if (k == 1 || cost < best_cost * 0.97) {
       best = k;
@@ -870,8 +856,6 @@ int launch_ssd(const void *x, const float *dt, const float *A, const void *Bm, c
     tdt = tx;  // never used by the kernels
   }
   float *seg_totals = nullptr, *seg_states = nullptr;
-  NB200_REQUIRE(plan.nseg == 1 || plan.steps_per_seg <= kSegMaxSteps, NB200_ERR_UNSUPPORTED,
-                "ssd_chunk_scan: a segment of %d steps exceeds %d", plan.steps_per_seg, kSegMaxSteps);
   if (plan.nseg > 1) {
     const size_t slots = (size_t)B * H * (plan.nseg - 1);
     seg_totals = reinterpret_cast<float *>(workspace + 256);
@@ -879,15 +863,13 @@ int launch_ssd(const void *x, const float *dt, const float *A, const void *Bm, c
     NB200_CHECK_CUDA(cudaFuncSetAttribute(ssd_segment_state_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSegSmem));
     NB200_CHECK_CUDA(cudaFuncSetAttribute(ssd_segment_state_kernel<DT>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                           cudaSharedmemCarveoutMaxShared));
-    ssd_segment_state_kernel<DT><<<dim3(B * H * (plan.nseg - 1)), dim3(kSegThreads), kSegSmem, st>>>(
-        tx, tb, tdt, dt_by_tma, dt, A, L, H, G, plan.nseg, plan.steps_per_seg, seg_states, seg_totals, status);
-    NB200_CHECK_CUDA(cudaGetLastError());
-    ssd_chain_kernel<<<dim3(kStateFloats / 256, B * H), dim3(256), 0, st>>>(seg_states, seg_totals, plan.nseg - 1);
+    ssd_segment_state_kernel<DT><<<dim3(B * (H / plan.lanes) * (plan.nseg - 1)), dim3(kSegThreads), kSegSmem, st>>>(
+        tx, tb, tdt, dt_by_tma, dt, A, L, H, G, plan.lanes, plan.nseg, plan.steps_per_seg, seg_states, seg_totals, status);
     NB200_CHECK_CUDA(cudaGetLastError());
   }
   NB200_CHECK_CUDA(cudaFuncSetAttribute(ssd_fused_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSsdSmem));
   ssd_fused_kernel<DT><<<dim3(B * (H / plan.lanes) * plan.nseg), dim3(kSsdThreads), kSsdSmem, st>>>(
-      tx, tb, tc, ty, tdt, dt_by_tma, dt, A, L, H, G, plan.lanes, plan.nseg, plan.steps_per_seg, seg_states, status);
+      tx, tb, tc, ty, tdt, dt_by_tma, dt, A, L, H, G, plan.lanes, plan.nseg, plan.steps_per_seg, seg_states, seg_totals, status);
   NB200_CHECK_CUDA(cudaGetLastError());
   return NB200_OK;
 }
@@ -943,7 +925,7 @@ extern "C" size_t nb200_ssd_workspace_bytes(int B, int L, int H, int P, int N, i
 
 extern "C" int nb200_ssd_launches(int B, int L, int H, int P, int N, int G, int chunk) {
   if (!ssd_shape_ok(B, L, H, P, N, G, chunk)) return 0;
-  return ssd_plan_for(B, L, H, G).nseg > 1 ? 3 : 1;
+  return ssd_plan_for(B, L, H, G).nseg > 1 ? 2 : 1;
 }
 
 extern "C" int nb200_ssd_chunk_scan_fwd(const void *x, const float *dt, const float *A, const void *Bm,

@@ -205,7 +205,7 @@ def ssd_workspace_bytes(B, L, H, P, N, G, chunk) -> int:
 
 
 def ssd_launches(B, L, H, P, N, G, chunk) -> int:
-    """Kernel launches one SSD call makes on the current device (3 when the sequences are cut into segments)."""
+    """Kernel launches one SSD call makes on the current device (2 when the sequences are cut into segments)."""
     return native.lib().nb200_ssd_launches(B, L, H, P, N, G, chunk)
 
 

@@ -337,7 +337,7 @@ def test_ssd_head_count_not_a_multiple_of_four(cuda, native_lib):
 @pytest.mark.parametrize("segments,H,G", [(2, 4, 1), (3, 4, 2), (8, 4, 1), (4, 3, 1), (2, 6, 2)])
 def test_ssd_sequences_cut_into_segments(cuda, native_lib, monkeypatch, segments, H, G):
     """A sequence cut into segments that run as separate CTAs: the state entering each later segment comes from
-    the segment-state and chain kernels.  NB200_SSD_SEGMENTS forces the cut that the library would only choose
+    the segment-state kernel and the recurrence over its results.  NB200_SSD_SEGMENTS forces the cut that the library would only choose
     for a problem with few (batch, head) pairs.  Head counts 3 and 6 with 2 groups run one head per CTA (no pair
     shares B and C); 8 segments of a 1024-row sequence are one step each."""
     from neptune_mlir import runtime
@@ -349,7 +349,7 @@ def test_ssd_sequences_cut_into_segments(cuda, native_lib, monkeypatch, segments
     outs = {}
     for k in (1, segments):
         monkeypatch.setenv("NB200_SSD_SEGMENTS", str(k))
-        assert runtime.ssd_launches(B, L, H, P, N, G, chunk) == (1 if k == 1 else 3)
+        assert runtime.ssd_launches(B, L, H, P, N, G, chunk) == (1 if k == 1 else 2)
         y = torch.full((B, L, H, P), float("nan"), dtype=torch.bfloat16, device=cuda)
         runtime.ssd_chunk_scan(*dev_args, ws, y, B=B, L=L, H=H, P=P, N=N, G=G, chunk=chunk, dtype="bf16")
         finish()
