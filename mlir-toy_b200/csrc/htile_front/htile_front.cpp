@@ -1200,7 +1200,8 @@ class Printer {
   }
   static std::string list(const Attr &a) {  // the bracketed form of permutation / mask / dimensions
     std::string o = "[";
-    for (size_t k = 0; k < a.arr.size(); ++k) o += (k ? ", " : "") + std::to_string(a.arr[k].i);
+    for (size_t k = 0; k < a.arr.size(); ++k)   // a mask is an array of booleans, the others of integers
+      o += (k ? ", " : "") + (a.arr[k].kind == Attr::Bool ? std::string(a.arr[k].b ? "true" : "false") : std::to_string(a.arr[k].i));
     return o + "]";
   }
   static std::string attr_dict(const AttrDict &d, const std::set<std::string> &skip) {

@@ -774,7 +774,8 @@ def print_module(module: Module) -> str:
                          f" : {tys[0]} -> {op.result.type}")
         elif n in ("htile.permute", "htile.unsqueeze"):
             key = "permutation" if n == "htile.permute" else "mask"
-            lines.append(f"{lhs}{n} {ops[0]} {key} {a[key]}{_fmt_attr_dict(a, (key,))} : {tys[0]} -> {op.result.type}")
+            items = ", ".join(("true" if x else "false") if isinstance(x, bool) else str(x) for x in a[key])
+            lines.append(f"{lhs}{n} {ops[0]} {key} [{items}]{_fmt_attr_dict(a, (key,))} : {tys[0]} -> {op.result.type}")
         elif n in ("htile.full", "htile.copy"):
             lines.append(f"{lhs}{n} {ops[0]}{_fmt_attr_dict(a)} : {tys[0]} -> {op.result.type}")
         elif n == "htile.arange":

@@ -16,6 +16,10 @@ function onto one hand-written kernel family.  It therefore *recognises* program
   f16 / bf16 / f32, optional causal mask written with htile.arange + arith.cmpi + arith.select);
   the function's expression graph is compared with the recurrence, and shapes, scale constant and
   causality are read off it;
+* split-K flash-decoding with its log-sum-exp combine spelled in HTile ops (two ``gpu.launch`` regions:
+  the per-split online softmax of the grouped query heads, then the merge of the partials;
+  ``neptune_mlir.programs.decode_splitk_htile`` writes it): both regions are compared with the operator's
+  equations and B, Hq, Hkv, L, D, the split count and the scale are read off them;
 * operator declarations: a ``func.func`` with attribute ``htile.operator`` naming one of
   ``decode_splitk``, ``selective_scan``, ``ssd_chunk_scan`` and an empty body; the memref
   argument types carry the problem sizes.  The dialect has no scan op
@@ -56,6 +60,8 @@ class _Graph:
 
     def __init__(self, func: ht.Func):
         self.func = func
+        # block ids of the first gpu.launch are ("bid", i); those of launch k > 0 are ("bid", i, k)
+        self._launch_no = {id(op): k for k, op in enumerate(o for o in func.body.operations if o.name == "gpu.launch")}
         self._memo: dict[int, tuple] = {}
 
     def of(self, v: ht.Value) -> tuple:
@@ -72,7 +78,10 @@ class _Graph:
                 return ("arg", v.index)
             if parent.name == "gpu.launch":
                 kinds = ("bid", "bid", "bid", "tid", "tid", "tid")
-                return (kinds[v.index], v.index % 3) if v.index < 6 else ("launch_size", v.index - 6)
+                which = self._launch_no.get(id(parent), 0)
+                if v.index >= 6:
+                    return ("launch_size", v.index - 6)
+                return (kinds[v.index], v.index % 3) if which == 0 else (kinds[v.index], v.index % 3, which)
             if parent.name == "scf.for":
                 return ("iv", id(parent)) if v.index == 0 else ("iter", id(parent), v.index - 1)
             raise _unsupported(f"block argument of {parent.name}")
@@ -105,6 +114,8 @@ class _Graph:
             return ("reduce", op.attributes["kind"], op.attributes["axis"], self.of(op.operands[0]))
         if n == "htile.arange":
             return ("arange", self.of(op.operands[0]), self.of(op.operands[1]))
+        if n == "htile.unsqueeze":
+            return ("unsqueeze", tuple(bool(b) for b in op.attributes["mask"]), self.of(op.operands[0]))
         if n == "arith.truncf":
             return ("truncf", v.type.element_type.name, self.of(op.operands[0]))
         if n in ("arith.cmpi", "arith.cmpf"):
@@ -162,6 +173,8 @@ class Translator:
         operator = fn.attributes.get("htile.operator")
         if operator is not None:
             stmt = self._declared_operator(fn, operator, params)
+        elif sum(1 for op in fn.body.operations if op.name == "gpu.launch") == 2:
+            stmt = self._decode_program(fn, params)
         else:
             stmt = self._attention(fn, params)
         return function_def(fn.name, params, [stmt])
@@ -239,6 +252,124 @@ class Translator:
             chunk = int(fn.attributes.get("chunk", 256))
             return self._runtime_call("ssd_chunk_scan", params, B=B, L=L, H=H, P=P, N=N, G=G, chunk=chunk, dtype=dts[0])
         raise _unsupported(f"@{fn.name}: unknown htile.operator '{operator}'")
+
+    # --- split-K decode and its combine, spelled in HTile ops ---
+
+    def _decode_program(self, fn: ht.Func, params: list[str]) -> ast.stmt:
+        def need(cond: bool, what: str) -> None:
+            if not cond:
+                raise _unsupported(f"@{fn.name}: not the split-K decode program this target implements ({what})")
+
+        for op in fn.body.walk():
+            if op.name == "htile.dot":
+                reject_dot_transpose_attrs(op, "B200")
+        launches = [op for op in fn.body.operations if op.name == "gpu.launch"]
+        others = [op for op in fn.body.operations if op.name not in ("gpu.launch", "arith.constant", "return", "func.return")]
+        need(len(launches) == 2 and not others and len(fn.arguments) == 5, "five memrefs, constants and two gpu.launch regions")
+        g = _Graph(fn)
+        q_ty, k_ty, v_ty, p_ty, o_ty = (a.type for a in fn.arguments)
+        need(len(q_ty.shape) == 3 and len(k_ty.shape) == 4 and k_ty.shape == v_ty.shape and o_ty.shape == q_ty.shape,
+             "q/out [B,Hq,D], k/v [B,Hkv,L,D]")
+        B, Hq, D = q_ty.shape
+        Hkv, L = k_ty.shape[1], k_ty.shape[2]
+        dtype = q_ty.element_type.name
+        need(k_ty.shape[0] == B and k_ty.shape[3] == D and Hq % Hkv == 0, "consistent extents")
+        need(dtype in ("f16", "bf16") and all(t.element_type.name == dtype for t in (k_ty, v_ty, o_ty)), "q/k/v/out share f16 or bf16")
+        need(len(p_ty.shape) == 4 and p_ty.shape[:2] == (B, Hq) and p_ty.shape[3] == D + 2 and p_ty.element_type.name == "f32",
+             "partials memref<BxHqxSx(D+2)xf32>")
+        S = p_ty.shape[2]
+        need(L % S == 0, "equal splits")
+        G, T = Hq // Hkv, L // S
+        c0 = ("const", 0)
+
+        # ---- first region: one block per (split, kv head, sequence)
+        first, second = launches
+        body = first.regions[0]
+        stores = [op for op in body.operations if op.name == "htile.store"]
+        fors = [op for op in body.operations if op.name == "scf.for"]
+        need(len(stores) == 3 and len(fors) == 1, "one kv loop and three stores (o, m, l) in the first region")
+        need([_const_int(g.of(o), "grid size") for o in first.operands[:3]] == [S, Hkv, B], "grid (splits, kv heads, batch)")
+        loop = fors[0]
+        lid = id(loop)
+        h0, t0 = _mul(("bid", 1), ("const", G)), _mul(("bid", 0), ("const", T))
+        by_col = {}
+        for st in stores:
+            need(g.of(st.operands[1]) == ("arg", 3), "the first region stores into partials")
+            offs = tuple(g.of(o) for o in st.operands[2:])
+            need(len(offs) == 4 and offs[:3] == (("bid", 2), h0, ("bid", 0)) and offs[3][0] == "const",
+                 "partials written at [bz, by*G, bx, column]")
+            by_col[offs[3][1]] = g.of(st.operands[0])
+        need(set(by_col) == {0, D, D + 1}, "columns 0 (o), D (m) and D+1 (l)")
+
+        def carried(expr, mask):
+            need(expr[0] == "unsqueeze" and expr[1] == mask and expr[2][:2] == ("for", lid), "stores of the loop's results")
+            return expr[2][2]
+
+        k_acc = carried(by_col[0], (False, True, False))
+        k_m, k_l = carried(by_col[D], (False, True, True)), carried(by_col[D + 1], (False, True, True))
+        need({k_acc, k_m, k_l} == {0, 1, 2}, "o, m, l are the three carried tiles")
+        lb, ub, step = (_const_int(g.of(o), "loop bound") for o in loop.operands[:3])
+        need(lb == 0 and step == 1 and ub > 0 and len(loop.results) == 3, "for j = 0 to N step 1 with three carried tiles")
+        inits = [g.of(o) for o in loop.operands[3:]]
+        need(inits[k_acc] == ("const", 0.0) and inits[k_l] == ("const", 0.0), "o and l start at zero")
+        need(inits[k_m][0] == "const" and inits[k_m][1] < -1e30, "running maximum starts at -FLT_MAX")
+        yld = loop.regions[0].operations[-1]
+        need(yld.name == "scf.yield" and len(yld.operands) == 3, "loop ends in scf.yield of three tiles")
+        y = [g.of(o) for o in yld.operands]
+        it_acc, it_l, it_m = ("iter", lid, k_acc), ("iter", lid, k_l), ("iter", lid, k_m)
+        m_new = y[k_m]
+        need(m_new[0] == "arith.maximumf" and it_m in m_new[1:], "m' = max(m, rowmax S)")
+        red = m_new[1] if m_new[2] == it_m else m_new[2]
+        need(red[:3] == ("reduce", "max", 1), "row maximum over axis 1")
+        Sx = red[3]
+        need(Sx[0] == "arith.mulf", "scores scaled by a constant")
+        scale_c = next((a for a in Sx[1:] if a[0] == "const"), None)
+        qk = next((a for a in Sx[1:] if a[0] == "dot"), None)
+        need(scale_c is not None and qk is not None and isinstance(scale_c[1], float), "S = dot(Q, K) * c")
+        q_load, k_load = qk[1], qk[2]
+        need(q_load[0] == "load" and k_load[0] == "load" and not qk[3] and not qk[4], "dot of two loaded tiles")
+        need(q_load[1] == ("arg", 0) and q_load[2] == (("bid", 2), h0, c0) and q_load[4] == (G, D) and q_load[3] == (0, 1),
+             "Q tile [G, D]: the query heads of the kv head's group")
+        need(k_load[3] == (1, 0), "K tile read through dimension_order [1, 0] (K^T)")
+        tile_n = k_load[4][1]
+        need(ub * tile_n == T, "the loop covers the split's rows")
+        rows = _c("arith.addi", t0, _mul(("iv", lid), ("const", tile_n)))
+        kv_offsets = (("bid", 2), ("bid", 1), rows, c0)
+        need(k_load[1] == ("arg", 1) and k_load[2] == kv_offsets and k_load[4] == (D, tile_n), "K tile [BN, D] at [bz, by, bx*T + j*BN, 0]")
+        P = _c("math.exp2", _c("arith.subf", Sx, m_new))
+        alpha = _c("math.exp2", _c("arith.subf", it_m, m_new))
+        need(y[k_l] == _c("arith.addf", _c("arith.mulf", it_l, alpha), ("reduce", "sum", 1, P)), "l' = l * 2^(m - m') + rowsum 2^(S - m')")
+        acc_new = y[k_acc]
+        need(acc_new[0] == "arith.addf", "o' = o * 2^(m - m') + P V")
+        pv = next((a for a in acc_new[1:] if a[0] == "dot"), None)
+        rest = next((a for a in acc_new[1:] if a[0] != "dot"), None)
+        need(pv is not None and rest == _c("arith.mulf", it_acc, alpha), "o rescaled by 2^(m - m')")
+        need(pv[1] == P and not pv[3] and not pv[4] and pv[2][0] == "arith.extf", "P (fp32) times V extended to fp32")
+        v_load = pv[2][1]
+        need(v_load[0] == "load" and v_load[1] == ("arg", 2) and v_load[2] == kv_offsets and v_load[4] == (tile_n, D)
+             and v_load[3] == (0, 1), "V tile [BN, D] at the K tile's offsets")
+
+        # ---- second region: one block per (query head, sequence) merges the splits
+        body2 = second.regions[0]
+        stores2 = [op for op in body2.operations if op.name == "htile.store"]
+        need(len(stores2) == 1 and not [op for op in body2.operations if op.name == "scf.for"], "one store and no loop in the second region")
+        need([_const_int(g.of(o), "grid size") for o in second.operands[:3]] == [Hq, B, 1], "grid (query heads, batch, 1)")
+        st = stores2[0]
+        cx, cy = ("bid", 0, 1), ("bid", 1, 1)
+        need(g.of(st.operands[1]) == ("arg", 4) and tuple(g.of(o) for o in st.operands[2:]) == (cy, cx, c0)
+             and tuple(st.operands[0].type.shape) == (1, D), "out[b, h, :] written as a [1, D] tile")
+
+        def part(col, shape):
+            return ("load", ("arg", 3), (cy, cx, c0, ("const", col)), tuple(range(len(shape))), shape)
+
+        o_l, m_l, l_l = part(0, (S, D)), part(D, (S, 1)), part(D + 1, (S, 1))
+        w = _c("math.exp2", _c("arith.subf", m_l, ("reduce", "max", 0, m_l)))
+        num = ("reduce", "sum", 0, _c("arith.mulf", o_l, ("reduce", "sum", 1, w)))
+        den = ("reduce", "sum", 0, _c("arith.mulf", w, l_l))
+        want = ("truncf", dtype, _c("arith.divf", ("unsqueeze", (True, False), num), den))
+        need(g.of(st.operands[0]) == want, "out = sum_s 2^(m_s - M) o_s / sum_s 2^(m_s - M) l_s, rounded to the storage dtype")
+        return self._runtime_call("decode_splitk", params, B=B, Hq=Hq, Hkv=Hkv, L=L, D=D, n_splits=S, dtype=dtype,
+                                  scale_log2=scale_c[1])
 
     # --- the FlashAttention recurrence ---
 

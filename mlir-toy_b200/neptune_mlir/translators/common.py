@@ -64,7 +64,8 @@ def function_def(fn_name: str, params: list[str], body: list[ast.stmt], doc: str
 # ---------------------------------------------------------------------------
 
 def dot_transpose_attrs(op: ht.Op) -> list[str]:
-    return [n for n in ("transpose_a", "transpose_b") if op.attributes.get(n)]
+    # presence decides, as in the reference (common.py:179-184): a unit attribute has no value to test
+    return [n for n in ("transpose_a", "transpose_b") if op.attributes.get(n) is not None]
 
 
 def reject_dot_transpose_attrs(op: ht.Op, backend: str) -> None:

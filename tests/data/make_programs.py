@@ -33,6 +33,7 @@ PROGRAMS = {
     "attention_causal_f32_1x4x256x64": programs.attention_htile("attention_causal_f32", 1, 4, 256, 64, "f32", causal=True),
     "attention_causal_bf16_8x32x4096x128": programs.attention_htile("attention_causal_bf16", 8, 32, 4096, 128, "bf16", causal=True),
     "decode_splitk_bf16_64x32x8x32768x128": programs.decode_splitk_decl("decode_splitk_bf16", 64, 32, 8, 32768, 128, 16),
+    "decode_splitk_htile_bf16_64x32x8x32768x128": programs.decode_splitk_htile("decode_splitk_htile_bf16", 64, 32, 8, 32768, 128, 16),
     "selective_scan_bf16_8x4096x4096": programs.selective_scan_decl("selective_scan_bf16", 8, 4096, 4096, 16),
     "ssd_chunk_scan_bf16_4x8192x64x64": programs.ssd_chunk_scan_decl("ssd_chunk_scan_bf16", 4, 8192, 64, 64, 128, 1, 256, SSD_WS),
 }

@@ -27,7 +27,7 @@ check, by the Python reader and pass -- wrapped in the stand-in's object model a
    beside this build's kernel on a machine that has no copy of the reference tree.
 
 Usage (needs the reference tree; run from the repository root):
-    python tests/golden/make_reference_translations.py /path/to/reference [--emit-only]
+    python tests/golden/make_reference_translations.py /path/to/reference [--emit-only | --check-only]
 """
 
 import ast
@@ -133,8 +133,9 @@ def run_source(source: str, name: str, grid, *tensors) -> None:
 EMITTED_PROGRAM = "attention_f16_1x32x4096x128"
 
 
-def emit_reference_modules(ref) -> None:
-    """What the three reference translators emit for this build's spelling of the reference-shape program."""
+def emit_reference_modules(ref, check_only: bool = False) -> None:
+    """What the three reference translators emit for this build's spelling of the reference-shape program;
+    with ``check_only`` the stored files are compared with it instead of being rewritten."""
     text = (ROOT / "tests" / "data" / f"{EMITTED_PROGRAM}.mlir").read_text()
     out_dir = HERE / "reference_emitted"
     out_dir.mkdir(exist_ok=True)
@@ -143,8 +144,14 @@ def emit_reference_modules(ref) -> None:
         header = (f"# Emitted by the reference project's {name} translator (imported unmodified from the reference tree)\n"
                   f"# for tests/data/{EMITTED_PROGRAM}.mlir; written by tests/golden/make_reference_translations.py.\n"
                   "# Not product code: the benchmark launches it as the reference's own GPU path.\n")
-        (out_dir / f"{EMITTED_PROGRAM}_{name}.py").write_text(header + source + "\n")
-        print(f"wrote reference_emitted/{EMITTED_PROGRAM}_{name}.py ({len(source.splitlines())} lines)")
+        path = out_dir / f"{EMITTED_PROGRAM}_{name}.py"
+        if check_only:
+            if path.read_text() != header + source + "\n":
+                raise SystemExit(f"reference_emitted/{path.name} is not what the reference's {name} translator emits now")
+            print(f"reference_emitted/{path.name} is current")
+            continue
+        path.write_text(header + source + "\n")
+        print(f"wrote reference_emitted/{path.name} ({len(source.splitlines())} lines)")
 
 
 def main() -> None:
@@ -154,8 +161,8 @@ def main() -> None:
     ref_root = Path(args[0] if args else os.environ["NEPTUNE_REFERENCE_ROOT"])
     ref = load_reference_translator(ref_root)
     check_standin(ref, ref_root)
-    emit_reference_modules(ref)
-    if "--emit-only" in sys.argv:
+    emit_reference_modules(ref, check_only="--check-only" in sys.argv)
+    if "--emit-only" in sys.argv or "--check-only" in sys.argv:
         return
     ref_triton = ref["triton"]
 

@@ -19,6 +19,8 @@ def _built_programs():
     yield "attention_nc", programs.attention_htile("a", 2, 4, 512, 128, "f16", causal=False)
     yield "attention_causal", programs.attention_htile("b", 1, 4, 256, 64, "f32", causal=True)
     yield "decode", programs.decode_splitk_decl("d", 2, 8, 2, 1024, 128, 4)
+    yield "decode_htile", programs.decode_splitk_htile("dh", 2, 8, 2, 1024, 128, 4)
+    yield "decode_htile_f16", programs.decode_splitk_htile("dh16", 1, 16, 2, 2048, 128, 8, "f16", tile_n=128)
     yield "scan", programs.selective_scan_decl("s", 2, 64, 256, 16)
     yield "ssd", programs.ssd_chunk_scan_decl("m", 1, 512, 4, 64, 128, 1, 256, 16)
 

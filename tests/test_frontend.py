@@ -143,6 +143,31 @@ def test_paged_decode_declaration(tmp_path, monkeypatch):
         b200.translate_file(str(path))
 
 
+def test_decode_program_spelled_in_htile_ops_is_recognised(tmp_path):
+    """Split-K decode + combine written with load / dot / reduce / exp2 / unsqueeze / store (two gpu.launch regions)
+    maps to the same call as the operator declaration; edits that change its meaning are refused."""
+    good = programs.decode_splitk_htile("dec", 2, 8, 2, 1024, 128, 4)
+    path = tmp_path / "dec.mlir"
+    path.write_text(good)
+    src = ast.unparse(b200.translate_file(str(path)))
+    assert "nb200.decode_splitk(ptr_0, ptr_1, ptr_2, ptr_3, ptr_4, B=2, Hq=8, Hkv=2, L=1024, D=128, n_splits=4, " \
+           "dtype='bf16', scale_log2=0.127517431974411)" in src
+    decl = tmp_path / "decl.mlir"
+    decl.write_text(programs.decode_splitk_decl("dec", 2, 8, 2, 1024, 128, 4))
+    assert ast.unparse(b200.translate_file(str(decl))).replace("0.1275174286422308", "X") == src.replace("0.127517431974411", "X")
+    for old, new, why in (
+            ("%col_l = arith.constant 129 : index", "%col_l = arith.constant 128 : index", "columns 0"),      # l stored over m
+            ("in (%gx = %splits, %gy = %kv_heads, %gz = %batch)", "in (%gx = %kv_heads, %gy = %splits, %gz = %batch)", "grid"),
+            ('%den = htile.reduce %wl axis 0 kind "sum"', '%den = htile.reduce %wl axis 0 kind "max"', "out = sum_s"),
+            ("%r0 = arith.addi %t0, %j0 : index", "%r0 = arith.addi %j0, %j0 : index", "K tile"),
+            ("%l_new = arith.addf %l_scaled, %p_sum", "%l_new = arith.addf %l, %p_sum", "l' = l"),
+    ):
+        assert old in good
+        path.write_text(good.replace(old, new))
+        with pytest.raises(NotImplementedError, match=why):
+            b200.translate_file(str(path))
+
+
 def test_syntax_errors_surface_as_runtime_error(tmp_path):
     path = tmp_path / "bad.mlir"
     path.write_text("func.func @f(%a: memref<?x4xf16>) { return }")
@@ -155,6 +180,26 @@ def test_reference_program_translates():
     src = ast.unparse(b200.translate_file(str(REFERENCE_PROGRAM)))
     assert "def flash_attention_htile(ptr_0, ptr_1, ptr_2, ptr_3):" in src
     assert "shape=(1, 32, 4096, 128), kv_len=4096, dtype='f16', scale_log2=0.12751743082459868, causal=False" in src
+
+
+@pytest.mark.skipif(not REFERENCE_PROGRAM.exists(), reason="reference tree not present")
+def test_unmodified_reference_translators_reproduce_their_own_goldens():
+    """The strongest pin of the front end: the reference's Triton, TileLang and cuTile translators, imported
+    unmodified and fed by this build's HTile reader (the C++ one and the Python twin) plus the dot-transpose pass
+    through the ``mlir.ir`` stand-in, emit the reference's three golden texts byte for byte
+    (tests/golden/flash_attention_{triton,tilelang,cutile}.py of the reference); and the emitted modules stored
+    for the benchmark's reference arm are what those translators emit today.  Runs in a child process because the
+    generator switches Triton to its interpreter."""
+    import subprocess
+    import sys
+
+    script = Path(__file__).parent / "golden" / "make_reference_translations.py"
+    ref_root = REFERENCE_PROGRAM.parents[2]
+    res = subprocess.run([sys.executable, str(script), str(ref_root), "--check-only"], capture_output=True, text=True,
+                         timeout=600)
+    assert res.returncode == 0, res.stdout + res.stderr
+    assert res.stdout.count("byte for byte") == 6          # three goldens x two front ends
+    assert res.stdout.count("is current") == 3
 
 
 def test_cli_prints_module(capsys, monkeypatch):

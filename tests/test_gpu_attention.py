@@ -60,6 +60,27 @@ def test_other_shapes_match_kernels_emitted_by_the_reference_translator(cuda, na
         torch.testing.assert_close(out.float().cpu(), want, rtol=0, atol=atol)
 
 
+@pytest.mark.parametrize("dtype,name,atol", [(torch.float16, "f16", REF_F16_ATOL), (torch.float32, "f32", F32_ATOL)])
+def test_level1_program_lowered_to_htile_runs(cuda, native_lib, dtype, name, atol):
+    """A Level-1 (scheduled tile IR) attention program goes through the L1 -> HTile lowering and the translator."""
+    import ast
+    import tempfile
+
+    from gpu_util import exec_translated_module
+    from neptune_mlir import l1, programs
+
+    B, H, S, D = (2, 4, 512, 128) if name == "f16" else (1, 4, 256, 64)
+    with tempfile.NamedTemporaryFile("w", suffix=".mlir", delete=False) as f:
+        f.write(programs.attention_l1("attn_from_l1", B, H, S, D, name))
+    mod = exec_translated_module(l1.translate_file(f.name), f"attn_from_l1_{name}")
+    assert isinstance(l1.translate_file(f.name), ast.Module)
+    q, k, v = inputs.attention_inputs(B, H, S, D, dtype, config=13)
+    out = torch.full((B, H, S, D), float("nan"), dtype=dtype, device=cuda)
+    mod.attn_from_l1(q.to(cuda), k.to(cuda), v.to(cuda), out)
+    finish()
+    torch.testing.assert_close(out.float().cpu(), attention.attention_reference(q, k, v), rtol=0, atol=atol)
+
+
 def test_config1_fp32_causal(cuda, native_lib):
     """B=1, H=4, S=256, D=64 fp32 causal (exact-fp32 kernel)."""
     q, k, v = inputs.attention_inputs(1, 4, 256, 64, torch.float32, config=1)

@@ -36,6 +36,27 @@ def test_decode_small_all_group_sizes(cuda, native_lib, Hq, Hkv):
     torch.testing.assert_close(p[..., :D], o, rtol=1e-3, atol=2e-3)
 
 
+@pytest.mark.parametrize("dtype,name,tile_n,atol", [(torch.bfloat16, "bf16", 64, 2e-2), (torch.float16, "f16", 128, 2e-3)])
+def test_decode_program_spelled_in_htile_ops(cuda, native_lib, dtype, name, tile_n, atol):
+    """The decode + combine program written op by op in HTile (two gpu.launch regions) runs through the translator
+    like the declaration does, partials included."""
+    from neptune_mlir import programs
+
+    B, Hq, Hkv, L, D, S = 2, 16, 4, 2048, 128, 8
+    q, k, v = inputs.decode_inputs(B=B, Hq=Hq, Hkv=Hkv, L=L, D=D, dtype=dtype)
+    mod = translate_text(programs.decode_splitk_htile("dec_prog", B, Hq, Hkv, L, D, S, name, tile_n=tile_n), f"dec_prog_{name}")
+    partials = torch.full((B, Hq, S, D + 2), float("nan"), device=cuda)
+    out = torch.full((B, Hq, D), float("nan"), dtype=dtype, device=cuda)
+    mod.dec_prog(q.to(cuda), k.to(cuda), v.to(cuda), partials, out)
+    finish()
+    assert_storage_close(out, decode.decode_reference(q, k, v), atol)
+    m, l, o = decode.decode_partials(q, k, v, S)
+    p = partials.cpu()
+    torch.testing.assert_close(p[..., D] / LOG2E, m, rtol=1e-4, atol=1e-4)
+    torch.testing.assert_close(p[..., D + 1], l, rtol=1e-3, atol=1e-3)
+    torch.testing.assert_close(p[..., :D], o, rtol=1e-3, atol=2e-3)
+
+
 def test_decode_ragged_split_and_f16(cuda, native_lib):
     """Split length 48 is not a multiple of the 64-row CTA step: the tail rows are masked."""
     from neptune_mlir import runtime
