@@ -507,28 +507,69 @@ def bench_extra(args, d: Dist, dev, flush, pk, pk_kind) -> dict:
             runtime.decode_combine(part, local, rows=rows, D=c["D"], n_splits=c["S"], row_stride=c["S"] * (c["D"] + 2),
                                    split_stride=c["D"] + 2, out_dtype="f32")
 
-        comm = gathered = None
+        comm = gathered = peer_ws = None
+        peer_note = None
         if d.world > 1:
             from neptune_mlir.nccl_comm import Communicator
             comm = Communicator.from_process_group()
             gathered = torch.empty((d.world, rows, c["D"] + 2), device=dev)
+            if args.merge != "nccl":
+                try:   # the merge as one kernel over peer-mapped memory; every rank must succeed or none uses it
+                    from neptune_mlir.peer import PeerWorkspace
+                    peer_ws = PeerWorkspace(rows, c["D"])
+                    ok_local = 1.0
+                except Exception as exc:  # noqa: BLE001
+                    peer_note, ok_local = f"{type(exc).__name__}: {str(exc)[:200]}", 0.0
+                flag = torch.tensor([ok_local], device=dev)
+                dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+                if flag.item() < 1.0:
+                    peer_ws = None
+
+        def merge_nccl():
+            runtime.decode_merge_nccl(local, gathered, o, rows=rows, D=c["D"], world=d.world, out_dtype="bf16", comm=comm)
 
         def merge_part():
-            if d.world > 1:
-                runtime.decode_merge_nccl(local, gathered, o, rows=rows, D=c["D"], world=d.world, out_dtype="bf16", comm=comm)
+            if d.world > 1 and peer_ws is not None:
+                peer_ws.merge(local, o, "bf16")
+            elif d.world > 1:
+                merge_nccl()
             else:
                 runtime.decode_combine(local, o, rows=rows, D=c["D"], n_splits=1, row_stride=c["D"] + 2,
                                        split_stride=c["D"] + 2, out_dtype="bf16")
 
+        # the whole of it as ONE launch per rank (split-K, local combine, push to the peers, wait, merge)
+        fused_ws = torch.zeros(lib.nb200_decode_sharded_workspace_bytes(c["Hq"], c["Hkv"], c["D"], c["S"]), dtype=torch.uint8, device=dev)
+        fused_gen = [0]
+
+        def fused_part():
+            if d.world > 1:
+                peer_ws.sharded_decode(q, k, v, fused_ws, o, Hq=c["Hq"], Hkv=c["Hkv"], L=Ll, D=c["D"], n_splits=c["S"], dtype="bf16",
+                                       scale_log2=scale_log2, out_dtype="bf16")
+            else:
+                st = torch.cuda.current_stream(dev).cuda_stream
+                native.check(lib.nb200_decode_sharded_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), fused_ws.data_ptr(), None, o.data_ptr(),
+                                                          c["Hq"], c["Hkv"], Ll, c["D"], c["S"], 1, scale_log2, 1, 0, 0, 1, 0,
+                                                          runtime.status_buffer(dev).data_ptr(), st), "decode_sharded_fwd")
+
+        use_fused = d.world == 1 or peer_ws is not None
         ms_stream = timed_steps(stream_part, steps, warm, flush, d)
+        ms_merge_nccl = timed_steps(merge_nccl, steps, warm, flush, d) if (d.world > 1 and peer_ws is not None) else None
         ms_merge = timed_steps(merge_part, steps, warm, flush, d)
-        ms_both = timed_steps(lambda: (stream_part(), merge_part()), steps, warm, flush, d)
+        ms_unfused = timed_steps(lambda: (stream_part(), merge_part()), steps, warm, flush, d)
+        ms_both = timed_steps(fused_part, steps, warm, flush, d) if use_fused else ms_unfused
         runtime.check_status(dev)
         total = 2 * c["Hkv"] * c["L"] * c["D"] * 2 + 2 * c["Hq"] * c["D"] * 2
         entry = record("decode_single_sequence", ms_both, total,
-                       {"config": f"B=1 L=262144 KV sharded along L over ranks, {c['S']} splits per rank (configs[2] variant)", "stream_ms": ms_stream,
+                       {"config": f"B=1 L=262144 KV sharded along L over ranks, {c['S']} splits per rank (configs[2] variant)",
+                        "launches_per_step": 1 if use_fused else 4,
+                        "how": ("nb200_decode_sharded_fwd: one launch per rank (split-K, local combine, push, bounded wait, merge)" if use_fused
+                                else "split-K + combine + NCCL all-gather + combine"),
+                        "unfused_ms": ms_unfused, "stream_ms": ms_stream,
                         "merge_ms": ms_merge, "merge_bytes_per_rank": rows * (c["D"] + 2) * 4,
-                        "collective": "ncclAllGather inside nb200_decode_merge_nccl" if d.world > 1 else "none"})
+                        "collective": ("none" if d.world == 1 else
+                                       "nb200_decode_merge_peer: one kernel, stores into peer-mapped buffers + flags (no NCCL on the data path)"
+                                       if peer_ws is not None else "ncclAllGather inside nb200_decode_merge_nccl"),
+                        "merge_ms_nccl_for_comparison": ms_merge_nccl, "peer_merge_unavailable": peer_note})
         # parity of the merged result at every rank count: each rank reduces its own KV slice with plain torch in
         # fp32 (scores, maximum, sums), the per-rank partials are gathered with torch.distributed and merged in
         # torch; the kernels' merged output must agree with that
@@ -561,6 +602,10 @@ def bench_extra(args, d: Dist, dev, flush, pk, pk_kind) -> dict:
             entry["parity"] = {"max_abs_err": err, "tolerance": BF16_ATOL,
                                "sample": f"the whole sequence on {d.world} rank(s) after the merge, against an fp32 torch evaluation "
                                          "of each rank's slice merged through torch.distributed (max over ranks)"}
+        if peer_ws is not None:
+            torch.cuda.synchronize(dev)
+            d.barrier()
+            peer_ws.close()
         if comm is not None:
             torch.cuda.synchronize(dev)
             comm.destroy()
@@ -790,6 +835,8 @@ def main() -> None:
     ap.add_argument("--skip-attention", action="store_true",
                     help="secondary workloads only (profiler captures of decode and the scans)")
     ap.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer end-to-end legs")
+    ap.add_argument("--merge", choices=("peer", "nccl"), default="peer",
+                    help="merge of the sharded single-sequence decode at N > 1: the peer-memory kernel (default) or NCCL")
     ap.add_argument("--third-party", action="store_true", help="also time third-party kernels of the image as yardsticks")
     ap.add_argument("--decode-batch", type=int, default=0,
                     help="batch of the split-K decode workload (default: the full 64); reduced for profiler captures")

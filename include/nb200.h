@@ -4,8 +4,8 @@
  * Every entry point takes raw device pointers, explicit extents, a dtype code and a CUDA stream
  * (a cudaStream_t passed as void*).  Calls are asynchronous on that stream and never synchronise
  * the device.  Nothing is allocated behind the caller's back: scratch memory is caller-provided
- * and sized by the matching *_workspace_bytes function (nb200_decode_fwd_static, which uses a fixed
- * array built into the library, is the one exception).  Every function that can fail returns an
+ * and sized by the matching *_workspace_bytes function (the exceptions are nb200_decode_fwd_static, which
+ * uses a fixed array built into the library, and nb200_peer_buffer_alloc, whose job is to allocate).  Every function that can fail returns an
  * int: 0 on success, a negative NB200_ERR_* code otherwise, with a thread-local message available
  * from nb200_last_error().  The library is safe to call from one host thread per GPU.
  *
@@ -160,6 +160,58 @@ int nb200_decode_paged_splitk(const void *q, const void *k_pages, const void *v_
 size_t nb200_decode_merge_workspace_bytes(int rows, int D, int world);
 int nb200_decode_merge_nccl(const float *local_partial, float *gathered, void *out, int rows, int D,
                             int world, int out_dtype, void *nccl_comm, void *stream);
+
+/*
+ * The same merge as ONE kernel over peer-mapped memory, without a library collective (no counterpart in the
+ * reference).  Every rank owns a symmetric buffer of nb200_decode_merge_peer_workspace_bytes(...) bytes, zeroed
+ * once and mapped into every other rank's address space; `peer_buffers` is a HOST array of `world` device
+ * pointers, entry r being rank r's buffer as this process sees it (entry `rank` is the rank's own).  The kernel
+ * stores this rank's partial into every rank's buffer with plain stores over NVLink, releases one flag per
+ * destination, waits until the partials of all ranks have arrived in its own buffer, and combines.  No multicast
+ * is used anywhere.
+ *
+ *   generation : the call's sequence number, the same on every rank, starting at 1 and growing by one per call
+ *                (the two halves of the buffer alternate with it, so calls need no clearing in between)
+ *   wait_ns    : limit of the wait for the other ranks' partials.  If it expires, `out` is left untouched and
+ *                status (NB200_STATUS_WORDS int32, zeroed by the caller, may be NULL) records code 31, the rank
+ *                that never arrived and the generation; nb200_status_read then returns NB200_ERR_DEVICE_TIMEOUT.
+ * All ranks must make the call, each on its own GPU; the kernels meet through the flags.
+ */
+size_t nb200_decode_merge_peer_workspace_bytes(int rows, int D, int world);
+int nb200_decode_merge_peer(const float *local_partial, void *const *peer_buffers, void *out, int rows, int D,
+                            int world, int rank, unsigned generation, int out_dtype, long long wait_ns,
+                            int *status, void *stream);
+
+/*
+ * The whole sharded single-sequence decode of one rank as ONE kernel launch: split-K over this rank's slice of
+ * the cache, the combine of its splits, the push of the rank's partial into every peer's buffer, the bounded
+ * wait for the others and the final merge -- the stages handed over by "the last CTA to finish does the next
+ * one" tickets, so no CTA waits for another CTA of the launch (no counterpart in the reference).
+ *
+ *   q : [1, Hq, D]   k, v : [1, Hkv, Lkv, D], this rank's slice   out : [Hq, D] in out_dtype ([Hq, D + 2] fp32 for NB200_F32)
+ *   workspace    : nb200_decode_sharded_workspace_bytes(...) bytes, 256-byte aligned, ZEROED ONCE by the caller
+ *                  before the first call (ticket counters that the kernel resets itself, the rank's partial, the
+ *                  per-split partials)
+ *   peer_buffers, generation, wait_ns, status : as for nb200_decode_merge_peer (buffers sized with rows = Hq);
+ *                  with world == 1 they are not used and the call is a one-launch decode of one sequence
+ * n_splits * Hkv CTAs are launched; choose n_splits so that they fill the GPU's resident slots (two per SM) once.
+ */
+size_t nb200_decode_sharded_workspace_bytes(int Hq, int Hkv, int D, int n_splits);
+int nb200_decode_sharded_fwd(const void *q, const void *k, const void *v, void *workspace, void *const *peer_buffers,
+                             void *out, int Hq, int Hkv, int Lkv, int D, int n_splits, int dtype, float scale_log2,
+                             int world, int rank, unsigned generation, int out_dtype, long long wait_ns, int *status,
+                             void *stream);
+
+/*
+ * Allocation and CUDA-IPC mapping of such a symmetric buffer: the only entry points of the library that
+ * allocate device memory, and they say so by name (a host with its own way of mapping peer memory does not
+ * need them).  alloc: cudaMalloc + clear + export a 64-byte handle; open: map another process's buffer from
+ * its handle (peer access is enabled on first use); close / free: undo them.  Synchronous; set-up time only.
+ */
+int nb200_peer_buffer_alloc(size_t bytes, void **ptr, unsigned char *handle64);
+int nb200_peer_buffer_open(const unsigned char *handle64, void **ptr);
+int nb200_peer_buffer_close(void *ptr);
+int nb200_peer_buffer_free(void *ptr);
 
 /*
  * Split-K decode plus combine for callers that may not allocate (no counterpart in the reference).

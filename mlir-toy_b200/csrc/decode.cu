@@ -17,6 +17,7 @@
 #include <mutex>
 
 #include "nb200_common.cuh"
+#include "peer_merge.cuh"
 #include "sm100_primitives.cuh"
 
 namespace nb200 {
@@ -302,12 +303,147 @@ __device__ __forceinline__ void bulk_load(uint32_t smem_dst, const void *gsrc, u
                : "memory");
 }
 
-template <int DT, int G>
+// ---- the sharded single-sequence decode as ONE kernel -------------------------------------------------------
+// When one sequence's cache is split along its length over the GPUs of a node, every GPU reduces its slice with the
+// split-K kernel above and the per-GPU results are merged.  With TAIL the ring kernel does all of it in one launch,
+// the hand-overs made by "the last CTA to finish does the next stage" tickets, so that no CTA ever waits for
+// another CTA of the launch:
+//   1. every CTA writes its split's partial, then takes a ticket of its kv head; the CTA that takes the head's last
+//      ticket combines the head's splits into this GPU's partial (o, m, l) for the G query heads of the group;
+//   2. it then takes a ticket of the launch; the CTA that takes the last one pushes the GPU's whole partial
+//      [Hq][D + 2] into every peer's gather area (plain stores over NVLink), releases the arrival flags, waits
+//      (bounded) for the other GPUs' partials in its own area and writes the merged, normalised output.
+// With world == 1 step 2 is only the normalisation, which makes the same launch a single-kernel decode of one
+// sequence on one GPU.  The ticket counters ([Hkv + 1] ints, zeroed once by the caller) are reset by the last CTA.
+struct DecodeTail {
+  float *local;            // [Hq][D + 2] fp32 scratch: this GPU's partial
+  int *counters;           // [Hkv + 1], zero between launches
+  peer::Ptrs peers;        // symmetric buffers of all ranks (unused when world == 1)
+  void *out;               // [Hq][D] in out_dtype (or [Hq][D + 2] fp32)
+  int world, rank, out_dtype;
+  unsigned generation;
+  long long wait_ns;
+  int *status;
+};
+
+template <int G>
+__device__ __forceinline__ void decode_tail(const DecodeTail &t, const float *partials, int Hkv, int n_splits, int hkv,
+                                            unsigned char *scratch) {
+  constexpr int kW = kDecodeWarps;                 // the eight consumer warps do the arithmetic
+  constexpr int kWarpsPerRow = kW / G;             // G <= 8
+  float(*sm_acc)[kHeadDim] = reinterpret_cast<float(*)[kHeadDim]>(scratch);
+  float *sm_l = reinterpret_cast<float *>(scratch + kW * kHeadDim * 4);
+  int *sm_flag = reinterpret_cast<int *>(scratch + kW * kHeadDim * 4 + 64);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int Hq = Hkv * G;
+
+  __threadfence();                                 // this CTA's partial is visible before its ticket is
+  __syncthreads();
+  if (tid == 0) sm_flag[0] = (atomicAdd(t.counters + hkv, 1) == n_splits - 1) ? 1 : 0;
+  __syncthreads();
+  if (!sm_flag[0]) return;
+  __threadfence();
+
+  // ---- stage 1: this kv head's splits -> the GPU's partial for its G rows; kWarpsPerRow warps share a row
+  if (warp < kW) {
+    const int g = warp / kWarpsPerRow, part = warp % kWarpsPerRow;
+    const float *base = partials + ((size_t)(hkv * G + g) * n_splits) * (kHeadDim + 2);
+    float M = -INFINITY;
+    for (int s = lane; s < n_splits; s += 32) M = fmaxf(M, __ldcg(base + (size_t)s * (kHeadDim + 2) + kHeadDim));
+#pragma unroll
+    for (int d = 16; d >= 1; d >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, d));
+    const float Ms = (M == -INFINITY) ? 0.f : M;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float lsum = 0.f;
+    constexpr int kU = 4;
+    for (int s0 = part; s0 < n_splits; s0 += kWarpsPerRow * kU) {
+      float4 o[kU];
+      float ms[kU], ls[kU];
+#pragma unroll
+      for (int u = 0; u < kU; ++u) {
+        const int sidx = s0 + u * kWarpsPerRow;
+        const float *ps = base + (size_t)(sidx < n_splits ? sidx : s0) * (kHeadDim + 2);
+        const float2 a = __ldcg(reinterpret_cast<const float2 *>(ps + lane * 4));
+        const float2 b2 = __ldcg(reinterpret_cast<const float2 *>(ps + lane * 4 + 2));
+        o[u] = make_float4(a.x, a.y, b2.x, b2.y);
+        ms[u] = __ldcg(ps + kHeadDim);
+        ls[u] = __ldcg(ps + kHeadDim + 1);
+      }
+#pragma unroll
+      for (int u = 0; u < kU; ++u) {
+        if (s0 + u * kWarpsPerRow < n_splits) {
+          const float w = ex2(ms[u] - Ms);
+          acc.x += w * o[u].x;
+          acc.y += w * o[u].y;
+          acc.z += w * o[u].z;
+          acc.w += w * o[u].w;
+          lsum += w * ls[u];
+        }
+      }
+    }
+    *reinterpret_cast<float4 *>(&sm_acc[warp][lane * 4]) = acc;
+    if (lane == 0) sm_l[warp] = lsum;
+    __syncwarp();
+    asm volatile("bar.sync 2, %0;" ::"r"(kW * 32) : "memory");
+    if (part == 0) {
+      for (int w = 1; w < kWarpsPerRow; ++w) {
+        const float4 a = *reinterpret_cast<const float4 *>(&sm_acc[warp + w][lane * 4]);
+        acc.x += a.x;
+        acc.y += a.y;
+        acc.z += a.z;
+        acc.w += a.w;
+        lsum += sm_l[warp + w];
+      }
+      float *dst = t.local + (size_t)(hkv * G + g) * (kHeadDim + 2);
+      *reinterpret_cast<float2 *>(dst + lane * 4) = make_float2(acc.x, acc.y);
+      *reinterpret_cast<float2 *>(dst + lane * 4 + 2) = make_float2(acc.z, acc.w);
+      if (lane == 0) {
+        dst[kHeadDim] = M;
+        dst[kHeadDim + 1] = lsum;
+      }
+    }
+  }
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) sm_flag[0] = (atomicAdd(t.counters + Hkv, 1) == Hkv - 1) ? 1 : 0;
+  __syncthreads();
+  if (!sm_flag[0]) return;
+  __threadfence();
+
+  // ---- stage 2: across the GPUs
+  const float *gathered = t.local;                 // world == 1: the "gather" is the local partial itself
+  if (t.world > 1) {
+    peer::push(t.local, t.peers, Hq, t.world, t.rank, t.generation, 0, t.world, tid, blockDim.x);
+    __threadfence_system();
+    __syncthreads();
+    if (tid < t.world) peer::release_flag(t.peers, Hq, t.world, t.rank, t.generation, tid);
+    if (tid == 0) sm_flag[1] = 0;
+    __syncthreads();
+    if (tid < t.world && !peer::wait_arrival(t.peers, Hq, t.world, t.rank, t.generation, tid, t.wait_ns, t.status)) sm_flag[1] = 1;
+    __syncthreads();
+    gathered = t.peers.buf[t.rank] + (t.generation & 1u) * peer::area_floats(Hq, t.world);
+  } else if (tid == 0) {
+    sm_flag[1] = 0;
+  }
+  __syncthreads();
+  if (!sm_flag[1]) {
+    const size_t slot = (size_t)Hq * (kHeadDim + 2);
+    for (int row = warp; row < Hq; row += blockDim.x / 32) {
+      if (t.out_dtype == NB200_BF16) peer::combine_row<NB200_BF16>(gathered, slot, t.world, row, t.out, lane);
+      else if (t.out_dtype == NB200_F16) peer::combine_row<NB200_F16>(gathered, slot, t.world, row, t.out, lane);
+      else peer::combine_row<NB200_F32>(gathered, slot, t.world, row, t.out, lane);
+    }
+  }
+  if (tid <= Hkv) t.counters[tid] = 0;             // ready for the next launch (also after an expired wait)
+}
+
+template <int DT, int G, bool TAIL = false>
 __global__ void __launch_bounds__(kRingThreads, (G >= 8 ? 1 : 2))
 decode_splitk_ring_kernel(const uint16_t *__restrict__ q, const uint16_t *__restrict__ k,
                           const uint16_t *__restrict__ v, float *__restrict__ partials, int Hkv, int Lkv,
                           int n_splits, float scale_log2, const int *__restrict__ block_table,
-                          const int *__restrict__ seq_lens, int max_pages, int num_pages, int *status) {
+                          const int *__restrict__ seq_lens, int max_pages, int num_pages, int *status,
+                          const DecodeTail tail = DecodeTail{}) {
   extern __shared__ __align__(128) unsigned char ring[];
   RingBarriers *bars = reinterpret_cast<RingBarriers *>(ring + kRingStages * 2 * kStageBytes);
   volatile int *abort_flag = &bars->abort_flag;
@@ -611,32 +747,70 @@ decode_splitk_ring_kernel(const uint16_t *__restrict__ q, const uint16_t *__rest
       dst[kHeadDim + 1] = lsum;
     }
   }
+  if constexpr (TAIL) {
+    __syncthreads();   // the merge scratch in `ring` is read no more
+    decode_tail<G>(tail, partials, Hkv, n_splits, hkv, ring);
+  }
 }
 
-// One warp per output row; lane handles 4 of the 128 elements.
+// One CTA of four warps per output row.  The partials of a row sit in memory that nothing has touched since the
+// split-K kernel wrote it, so every load costs a full memory latency: the kernel is organised to have them all in
+// flight at once instead of one per split.  Each warp first finds the row maximum with its lanes reading
+// different splits' maxima in parallel; then warp w accumulates splits w, w + 4, ... (lane = 4 of the 128
+// elements), four splits' loads issued before any is used; the four partial sums meet in shared memory.
+constexpr int kCombineWarps = 4;
 template <int ODT>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(kCombineWarps * 32)
 decode_combine_kernel(const float *__restrict__ partials, void *__restrict__ out, int rows, int n_splits,
                       long long row_stride, long long split_stride) {
-  const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  if (row >= rows) return;
+  __shared__ float sm_acc[kCombineWarps][kHeadDim];
+  __shared__ float sm_l[kCombineWarps];
+  const int row = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const float *base = partials + (size_t)row * row_stride;
   float M = -INFINITY;
-  for (int s = 0; s < n_splits; ++s) M = fmaxf(M, base[(size_t)s * split_stride + kHeadDim]);
+  for (int s = lane; s < n_splits; s += 32) M = fmaxf(M, base[(size_t)s * split_stride + kHeadDim]);
+#pragma unroll
+  for (int d = 16; d >= 1; d >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, d));
   const float Ms = (M == -INFINITY) ? 0.f : M;
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
   float lsum = 0.f;
-  for (int s = 0; s < n_splits; ++s) {
-    const float *ps = base + (size_t)s * split_stride;
-    const float w = ex2(ps[kHeadDim] - Ms);
-    const float2 o01 = *reinterpret_cast<const float2 *>(ps + lane * 4);
-    const float2 o23 = *reinterpret_cast<const float2 *>(ps + lane * 4 + 2);
-    acc.x += w * o01.x;
-    acc.y += w * o01.y;
-    acc.z += w * o23.x;
-    acc.w += w * o23.y;
-    lsum += w * ps[kHeadDim + 1];
+  constexpr int kU = 4;
+  for (int s0 = warp; s0 < n_splits; s0 += kCombineWarps * kU) {
+    float2 o01[kU], o23[kU];
+    float ms[kU], ls[kU];
+#pragma unroll
+    for (int u = 0; u < kU; ++u) {
+      const int s = s0 + u * kCombineWarps;
+      const float *ps = base + (size_t)(s < n_splits ? s : s0) * split_stride;
+      o01[u] = *reinterpret_cast<const float2 *>(ps + lane * 4);
+      o23[u] = *reinterpret_cast<const float2 *>(ps + lane * 4 + 2);
+      ms[u] = ps[kHeadDim];
+      ls[u] = ps[kHeadDim + 1];
+    }
+#pragma unroll
+    for (int u = 0; u < kU; ++u) {
+      if (s0 + u * kCombineWarps < n_splits) {
+        const float w = ex2(ms[u] - Ms);
+        acc.x += w * o01[u].x;
+        acc.y += w * o01[u].y;
+        acc.z += w * o23[u].x;
+        acc.w += w * o23[u].y;
+        lsum += w * ls[u];
+      }
+    }
+  }
+  *reinterpret_cast<float4 *>(&sm_acc[warp][lane * 4]) = acc;
+  if (lane == 0) sm_l[warp] = lsum;
+  __syncthreads();
+  if (warp != 0) return;
+#pragma unroll
+  for (int w = 1; w < kCombineWarps; ++w) {
+    const float4 a = *reinterpret_cast<const float4 *>(&sm_acc[w][lane * 4]);
+    acc.x += a.x;
+    acc.y += a.y;
+    acc.z += a.z;
+    acc.w += a.w;
+    lsum += sm_l[w];
   }
   if constexpr (ODT == NB200_F32) {
     float *dst = reinterpret_cast<float *>(out) + (size_t)row * (kHeadDim + 2);
@@ -752,6 +926,83 @@ extern "C" int nb200_decode_splitk(const void *q, const void *k, const void *v, 
   return fail(NB200_ERR_UNSUPPORTED, "decode_splitk: dtype %d (f16 and bf16 only)", dtype);
 }
 
+namespace {
+
+size_t sharded_local_offset(int Hkv) { return ((size_t)(Hkv + 1) * sizeof(int) + 255) / 256 * 256; }
+size_t sharded_partials_offset(int Hq, int Hkv) {
+  return sharded_local_offset(Hkv) + ((size_t)Hq * (kHeadDim + 2) * sizeof(float) + 255) / 256 * 256;
+}
+
+template <int DT, int GV>
+int launch_sharded(const void *q, const void *k, const void *v, float *partials, int Hkv, int Lkv, int n_splits,
+                   float scale_log2, int *status, const DecodeTail &tail, cudaStream_t st) {
+  NB200_CHECK_CUDA(cudaFuncSetAttribute(decode_splitk_ring_kernel<DT, GV, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingSmem));
+  NB200_CHECK_CUDA(cudaFuncSetAttribute(decode_splitk_ring_kernel<DT, GV, true>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                        cudaSharedmemCarveoutMaxShared));
+  decode_splitk_ring_kernel<DT, GV, true><<<dim3(n_splits, Hkv, 1), dim3(kRingThreads), kRingSmem, st>>>(
+      static_cast<const uint16_t *>(q), static_cast<const uint16_t *>(k), static_cast<const uint16_t *>(v), partials, Hkv, Lkv,
+      n_splits, scale_log2, nullptr, nullptr, 0, 0, status, tail);
+  NB200_CHECK_CUDA(cudaGetLastError());
+  return NB200_OK;
+}
+
+}  // namespace
+
+extern "C" size_t nb200_decode_sharded_workspace_bytes(int Hq, int Hkv, int D, int n_splits) {
+  if (Hq <= 0 || Hkv <= 0 || D != kHeadDim || n_splits <= 0 || Hq % Hkv != 0) return 0;
+  return sharded_partials_offset(Hq, Hkv) + (size_t)Hq * n_splits * (kHeadDim + 2) * sizeof(float);
+}
+
+extern "C" int nb200_decode_sharded_fwd(const void *q, const void *k, const void *v, void *workspace,
+                                        void *const *peer_buffers, void *out, int Hq, int Hkv, int Lkv, int D,
+                                        int n_splits, int dtype, float scale_log2, int world, int rank,
+                                        unsigned generation, int out_dtype, long long wait_ns, int *status,
+                                        void *stream) {
+  NB200_REQUIRE(q && k && v && workspace && out, NB200_ERR_BAD_ARG, "decode_sharded_fwd: null pointer");
+  NB200_REQUIRE(Hq > 0 && Hkv > 0 && Lkv > 0 && n_splits > 0 && world > 0 && rank >= 0 && rank < world, NB200_ERR_BAD_ARG,
+                "decode_sharded_fwd: bad extent or rank");
+  NB200_REQUIRE(D == kHeadDim, NB200_ERR_UNSUPPORTED, "decode_sharded_fwd: D = %d, only 128 is implemented", D);
+  NB200_REQUIRE(Hq % Hkv == 0 && n_splits <= Lkv && Hkv <= 65535, NB200_ERR_UNSUPPORTED, "decode_sharded_fwd: Hq %% Hkv != 0, or more splits than rows");
+  NB200_REQUIRE(world <= peer::kMaxWorld, NB200_ERR_UNSUPPORTED, "decode_sharded_fwd: at most %d ranks", peer::kMaxWorld);
+  NB200_REQUIRE(world == 1 || (peer_buffers && generation != 0 && wait_ns > 0), NB200_ERR_BAD_ARG,
+                "decode_sharded_fwd: several ranks need peer buffers, a generation >= 1 and a positive wait limit");
+  NB200_REQUIRE(aligned16(q) && aligned16(k) && aligned16(v) && (reinterpret_cast<uintptr_t>(workspace) & 255u) == 0 &&
+                    (reinterpret_cast<uintptr_t>(out) & (out_dtype == NB200_F32 ? 3u : 7u)) == 0,
+                NB200_ERR_BAD_ARG, "decode_sharded_fwd: q/k/v 16-byte, workspace 256-byte, out 8-byte aligned");
+  NB200_REQUIRE(out_dtype == NB200_BF16 || out_dtype == NB200_F16 || out_dtype == NB200_F32, NB200_ERR_UNSUPPORTED,
+                "decode_sharded_fwd: out_dtype %d", out_dtype);
+  auto *ws = static_cast<unsigned char *>(workspace);
+  DecodeTail tail{};
+  tail.counters = reinterpret_cast<int *>(ws);
+  tail.local = reinterpret_cast<float *>(ws + sharded_local_offset(Hkv));
+  float *partials = reinterpret_cast<float *>(ws + sharded_partials_offset(Hq, Hkv));
+  for (int r = 0; r < world && world > 1; ++r) {
+    NB200_REQUIRE(peer_buffers[r] && aligned16(peer_buffers[r]), NB200_ERR_BAD_ARG,
+                  "decode_sharded_fwd: buffer of rank %d is null or not 16-byte aligned", r);
+    tail.peers.buf[r] = static_cast<float *>(peer_buffers[r]);
+  }
+  tail.out = out;
+  tail.world = world;
+  tail.rank = rank;
+  tail.out_dtype = out_dtype;
+  tail.generation = generation;
+  tail.wait_ns = wait_ns;
+  tail.status = status;
+  auto st = static_cast<cudaStream_t>(stream);
+#define NB200_SHARDED(DTV)                                                                                             \
+  switch (Hq / Hkv) {                                                                                                  \
+    case 1: return launch_sharded<DTV, 1>(q, k, v, partials, Hkv, Lkv, n_splits, scale_log2, status, tail, st);         \
+    case 2: return launch_sharded<DTV, 2>(q, k, v, partials, Hkv, Lkv, n_splits, scale_log2, status, tail, st);         \
+    case 4: return launch_sharded<DTV, 4>(q, k, v, partials, Hkv, Lkv, n_splits, scale_log2, status, tail, st);         \
+    case 8: return launch_sharded<DTV, 8>(q, k, v, partials, Hkv, Lkv, n_splits, scale_log2, status, tail, st);         \
+    default: return fail(NB200_ERR_UNSUPPORTED, "decode_sharded_fwd: Hq/Hkv = %d not in {1,2,4,8}", Hq / Hkv);         \
+  }
+  if (dtype == NB200_BF16) { NB200_SHARDED(NB200_BF16) }
+  if (dtype == NB200_F16) { NB200_SHARDED(NB200_F16) }
+#undef NB200_SHARDED
+  return fail(NB200_ERR_UNSUPPORTED, "decode_sharded_fwd: dtype %d (f16 and bf16 only)", dtype);
+}
+
 extern "C" int nb200_decode_paged_splitk(const void *q, const void *k_pages, const void *v_pages,
                                          const int *block_table, const int *seq_lens, float *partials, int B,
                                          int Hq, int Hkv, int num_pages, int max_pages, int page_size, int D,
@@ -793,7 +1044,7 @@ extern "C" int nb200_decode_combine(const float *partials, void *out, int rows, 
   NB200_REQUIRE((reinterpret_cast<uintptr_t>(out) & (out_dtype == NB200_F32 ? 3u : 7u)) == 0, NB200_ERR_BAD_ARG,
                 "decode_combine: out must be %d-byte aligned", out_dtype == NB200_F32 ? 4 : 8);
   auto st = static_cast<cudaStream_t>(stream);
-  const dim3 grid((rows + 3) / 4), block(128);
+  const dim3 grid(rows), block(kCombineWarps * 32);
   switch (out_dtype) {
     case NB200_BF16: decode_combine_kernel<NB200_BF16><<<grid, block, 0, st>>>(partials, out, rows, n_splits, row_stride, split_stride); break;
     case NB200_F16: decode_combine_kernel<NB200_F16><<<grid, block, 0, st>>>(partials, out, rows, n_splits, row_stride, split_stride); break;

@@ -8,7 +8,7 @@ signature, so that a test can check the library exports all of them.
 from __future__ import annotations
 
 import ctypes
-from ctypes import c_char_p, c_float, c_int, c_longlong, c_size_t, c_void_p
+from ctypes import c_char_p, c_float, c_int, c_longlong, c_size_t, c_uint, c_void_p
 from pathlib import Path
 
 from .plugin import find_library_path
@@ -35,6 +35,16 @@ SYMBOLS: dict[str, tuple] = {
     "nb200_decode_merge_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
     "nb200_decode_merge_nccl": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
                                         c_void_p]),
+    "nb200_decode_merge_peer_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "nb200_decode_merge_peer": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_uint, c_int,
+                                        c_longlong, c_void_p, c_void_p]),
+    "nb200_decode_sharded_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
+    "nb200_decode_sharded_fwd": (c_int, [c_void_p] * 6 + [c_int] * 6 + [c_float, c_int, c_int, c_uint, c_int, c_longlong,
+                                                                       c_void_p, c_void_p]),
+    "nb200_peer_buffer_alloc": (c_int, [c_size_t, c_void_p, c_void_p]),
+    "nb200_peer_buffer_open": (c_int, [c_void_p, c_void_p]),
+    "nb200_peer_buffer_close": (c_int, [c_void_p]),
+    "nb200_peer_buffer_free": (c_int, [c_void_p]),
     "nb200_decode_fwd_static": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                         c_int, c_int, c_float, c_void_p]),
     "nb200_selective_scan_fwd": (c_int, [c_void_p] * 8 + [c_int] * 5 + [c_void_p]),

@@ -1,9 +1,8 @@
 """Worker of tests/test_gpu_multi.py: one rank of a single-sequence decode sharded along the KV length.
 
 Launched by ``python -m torch.distributed.run``; every rank draws the same seeded sequence on the CPU,
-takes its slice, runs split-K + local combine through the C ABI, merges across ranks once through
-``nb200_decode_merge_nccl`` and once through ``torch.distributed`` + ``nb200_decode_combine``, and compares
-both with the CPU oracle on the whole sequence.  Prints ``OK rank <r>`` on success.
+takes its slice, runs split-K + local combine through the C ABI, merges across ranks through ``nb200_decode_merge_nccl``, through ``torch.distributed`` + ``nb200_decode_combine`` and
+through the peer-memory kernel ``nb200_decode_merge_peer``, and compares them with the CPU oracle on the whole sequence.  Prints ``OK rank <r>`` on success.
 """
 
 import math
@@ -71,6 +70,30 @@ def main() -> int:
     assert torch.equal(out_c, out_t), "C-ABI merge and torch.distributed merge disagree"
     assert torch.equal(gathered, g), "gathered partials differ between the two routes"
     assert err_c <= 2e-2, f"max-abs-err {err_c} > 2e-2"
+
+    # the same merge as one kernel over peer-mapped memory (CUDA IPC), three calls in a row on the same buffers
+    from neptune_mlir.peer import PeerWorkspace
+    ws = PeerWorkspace(Hq, D)
+    for _ in range(3):
+        out_p = torch.full((Hq, D), float("nan"), device=dev, dtype=torch.bfloat16)
+        ws.merge(local, out_p, "bf16")
+        torch.cuda.synchronize(dev)
+        runtime.check_status(dev)
+        assert torch.equal(out_p, out_c), "peer-memory merge and NCCL merge disagree"
+    # and the rank's whole share as ONE launch: split-K, local combine, push, wait, merge
+    S1 = 9
+    wbytes = lib.nb200_decode_sharded_workspace_bytes(Hq, Hkv, D, S1)
+    wsp = torch.zeros(wbytes, dtype=torch.uint8, device=dev)
+    for _ in range(3):
+        out_s = torch.full((Hq, D), float("nan"), device=dev, dtype=torch.bfloat16)
+        ws.sharded_decode(qd, kd, vd, wsp, out_s, Hq=Hq, Hkv=Hkv, L=Ll, D=D, n_splits=S1, dtype="bf16", scale_log2=scale_log2,
+                          out_dtype="bf16")
+        torch.cuda.synchronize(dev)
+        runtime.check_status(dev)
+        err_s = (out_s.float().cpu() - ref).abs().max().item()
+        assert err_s <= 2e-2, f"one-launch sharded decode: max-abs-err {err_s}"
+    dist.barrier()
+    ws.close()
     torch.cuda.synchronize(dev)
     comm.destroy()
     dist.barrier()
