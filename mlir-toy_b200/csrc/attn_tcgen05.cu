@@ -1,35 +1,39 @@
-// Fused attention forward on Blackwell tensor cores (f16 / bf16 storage, D = 128).
+// Fused attention forward on Blackwell tensor cores: persistent CTAs, KV blocks of 128 rows, two softmax
+// warpgroups taking alternate blocks (f16 / bf16 storage, D = 128).
 //
-// One CTA computes a tile of 128 query rows of one (batch, head) against the KV sequence in blocks
-// of 64 rows, with the online softmax of the HTile program
-// (tests/data/flash_attention_htile.mlir:40-143 of the reference) kept in the exp2 domain.  The
-// three stages of a block -- S = Q K^T, softmax, O += P V -- run as a software pipeline, each stage on
-// warps of its own that meet only at mbarriers:
+// A CTA (one per SM) works through a list of tiles of 128 query rows.  The KV sequence of a tile is walked in blocks
+// of 128 rows; the blocks of all the CTA's tiles form one stream, numbered g = 0, 1, 2, ...:
 //
-//   warp 4, warp 7      TMA producers (one lane each): Q once and K(j); V(j).  Two 16 KB buffers per
-//   (one lane each)     operand (128-byte swizzled), re-armed when the MMA that read a buffer has
-//                       retired.  Separate threads because K(j+1) is wanted a whole block before
-//                       V(j+1): one thread waiting for the V buffer would hold the K load back
-//   warp 5 (one lane)   QK issuer, operand descriptors built once: S = Q K(j)^T (8 x tcgen05.mma
-//                       128x64x16, both operands in smem) into TMEM columns 0..63.  The softmax warps
-//                       copy S(j-1) into registers first thing and release the buffer, so S(j) is
-//                       computed while they work on block j-1
-//   warp 6 (one lane)   PV issuer: O += P_b V(j) (4 x tcgen05.mma 128x128x16) with P read from TMEM
-//                       (two buffers of 32 columns, packed 16-bit) and V as an MN-major smem operand;
-//                       the accumulator O lives in TMEM columns 128..255.  A thread of its own, so
-//                       that a product is issued the moment P arrives instead of queueing behind
-//                       the score products of a later block
-//   warps 0-3           softmax: thread r owns row r (TMEM lane r), so row max and row sum need no
-//                       cross-thread traffic; the 64 scores are read from TMEM once into registers
-//                       (three-input maxima, packed f32x2 scale/sum, exp2, pack to 16 bit).
-//                       O is rescaled in TMEM only when a row maximum grows by more than 2^8,
-//                       which leaves the result unchanged (the same stale maximum scales P and
-//                       the running sum) but makes the rescale rare
+//   S(g) = Q K(g)^T      8 x tcgen05.mma 128x128x16, both operands in shared memory, into TMEM buffer g % 3
+//   softmax(g)           warpgroup g & 1 (thread = row = TMEM lane): scores to registers, row maximum, p = 2^(s - m),
+//                        P(g) as packed 16-bit over the first 64 columns of the same TMEM buffer
+//   O += P(g) V(g)       8 x tcgen05.mma 128x128x16 with P read from TMEM, O in TMEM columns 384..511
 //
-// Two CTAs are resident per SM (96 KB smem, 256 TMEM columns each).  Tiles are numbered so that
-// CTAs running at the same time work on the same few heads (K/V stay in L2) and, for causal
-// problems, the long tiles of a head are issued first.  Every wait is bounded; on expiry the CTA
-// records a code in the status words and unwinds.
+// The score products run up to three blocks ahead of the PV products (three S/P buffers): S(g+3) may start as
+// soon as PV(g) has retired, so between the end of QK(g) and the start of PV(g) the tensor pipe has other products
+// to do for about as long as the softmax of one block takes, and the two warpgroups together deliver a block per
+// two products.  Nothing of one block waits for anything but its own inputs, and the stream does not stop at tile
+// boundaries: while the last blocks of a tile are in the softmax, the score products of the next tile are already
+// running, and a fourth warpgroup writes the finished tile out.  Each product has an issuing thread of its own:
+// a tcgen05.mma costs its issuing thread 45-60 cycles and a commit or a barrier test 50-150, so a single thread
+// issuing both could not keep the pipe fed (measured: ~2000 cycles per block for sixteen 64-cycle products).
+//
+// Against blocks of 64 KV rows with two CTAs per SM, a 128x128x16 score product costs 64 cycles where two 128x64x16
+// cost 96: they are bound by operand reads from shared memory (128 B/clk), and Q is read half as often per FLOP.
+//
+// The running maximum of a row passes between the two warpgroups through shared memory (block g needs the value
+// block g-1 decided on); each keeps a partial row sum under the maximum it last used, and the epilogue combines
+// the two.  O is rescaled only when a maximum grows by more than 2^8.
+//
+//   warps 0-3 / 4-7  softmax of even / odd blocks           warps 8-11   epilogue (O / l -> global)
+//   warp 12, 15      TMA producers: Q and K; V (warp 15 also allocates the 512 TMEM columns)
+//   warp 13, 14      issuers of the score products and of the PV products (one lane each)
+//
+// Registers are moved from the producer / issuer / epilogue warps to the softmax warps with setmaxnreg (a softmax
+// thread holds the 128 scores of its row).  One CTA per SM: 192 KB of shared memory (two buffers of 32 KB each for
+// Q, K and V), all 512 TMEM columns.  No multicast anywhere.
+//
+// Every wait is bounded; on expiry the CTA records a code in the status words and unwinds.
 #include <cuda.h>
 
 #include "nb200_common.cuh"
@@ -40,27 +44,32 @@ namespace {
 
 using namespace sm100;
 
-constexpr int kBM = 128;            // query rows per CTA
-constexpr int kBN = 64;             // kv rows per pipeline step
-constexpr int kHeadGroup = 16;      // heads whose tiles are interleaved (tile-major) in the launch order
-constexpr int kD = 128;             // head dimension
-constexpr int kThreads = 256;       // 4 softmax warps, K producer, QK issuer, PV issuer, V producer
-constexpr int kQBytes = kBM * kD * 2;           // 32 KB: two 64-column boxes of 16 KB
-constexpr int kQBox = kQBytes / 2;
-constexpr int kKVBytes = kBN * kD * 2;          // 16 KB: two 64-column boxes of 8 KB
-constexpr int kKVBox = kKVBytes / 2;
-constexpr int kTmemCols = 256;                  // S (64) | P0 (32) | P1 (32) | O (128)
-constexpr int kSmemBytes = kQBytes + 4 * kKVBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
-constexpr float kRescaleThreshold = 8.0f;       // log2 units
+constexpr int kBM = 128;
+constexpr int kBN = 128;
+constexpr int kD = 128;
+constexpr int kHeadGroup = 16;
+constexpr int kThreads = 512;
+constexpr int kTileBytes = 128 * kD * 2;        // 32 KB: two 64-column boxes of 16 KB
+constexpr int kBox = kTileBytes / 2;
+constexpr int kSBufs = 3;
+constexpr int kTmemCols = 512;                  // S/P 0 | S/P 1 | S/P 2 | O, 128 columns each
+constexpr int kTmemO = 384;
+constexpr float kRescaleThreshold = 8.0f;
 
 enum : int { kErrProducer = 1, kErrMma = 2, kErrSoftmax = 3, kErrEpilogue = 4 };
 
-struct Barriers {
-  uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full, s_free, p_full[2], pv_done[2], o_full;
+struct Shared {
+  uint64_t q_full[2], q_empty[2], k_full[2], k_empty[2], v_full[2], v_empty[2];
+  uint64_t s_full[kSBufs], p_full[kSBufs], pv_done[kSBufs];
+  uint64_t o_full, o_free, m_ready[2], lm_ready, lm_free;
   uint32_t tmem_base;
   int abort_flag;
   int skip;
+  int pad;
+  float mslot[2][128];      // running maximum decided by block g, slot g & 1
+  float lm[2][128][2];      // per warpgroup: (maximum last used, partial row sum) of the finished tile
 };
+constexpr int kSmemBytes = 6 * kTileBytes + 1024 + static_cast<int>(sizeof(Shared));
 
 __device__ __forceinline__ void report(int *status, int code, int detail) {
   if (status && atomicCAS(status, 0, code) == 0) {
@@ -70,65 +79,137 @@ __device__ __forceinline__ void report(int *status, int code, int detail) {
   }
 }
 
+// Polling wait (mbarrier.test_wait never suspends the thread): the waiter continues a few cycles after the phase
+// completes instead of the 200-300 a suspended thread takes to come back.  For the single issuing thread only.
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_poll(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+  if (mbar_test_wait(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+#pragma unroll 1
+  while (true) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+      if (mbar_test_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (globaltimer_ns() - t0 > kWaitLimitNs) {
+      *abort_flag = 1;
+      return false;
+    }
+  }
+}
+
+// tcgen05.mma with the shared-memory descriptors given as low word + common high word.
+__device__ __forceinline__ void umma_ss_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t hi, uint32_t idesc,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      ".reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %3};\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t"
+      "}"
+      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_ts_lo(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t hi, uint32_t idesc,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      ".reg .b64 db;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t"
+      "}"
+      ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+struct Problem {
+  int Sq, Skv, n_qtiles, n_units, group, causal, total;
+};
+struct Tile {
+  int bh, qt, nblk;
+};
+// Launch order: heads in groups, tile-major inside a group, longest causal tiles first.
+__device__ __forceinline__ Tile tile_of(const Problem &p, int i) {
+  const int per_group = p.group * p.n_qtiles;
+  const int grp = i / per_group, rem = i % per_group;
+  const int heads_here = min(p.group, p.n_units - grp * p.group);
+  const int qi = rem / heads_here;
+  Tile t;
+  t.bh = grp * p.group + rem % heads_here;
+  t.qt = p.causal ? (p.n_qtiles - 1 - qi) : qi;
+  const int last_col = p.causal ? min(p.Skv - 1, t.qt * kBM + (p.Skv - p.Sq) + kBM - 1) : p.Skv - 1;
+  t.nblk = last_col / kBN + 1;
+  return t;
+}
+
 template <int DT>
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, 1)
 attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                        const __grid_constant__ CUtensorMap tm_v, uint16_t *__restrict__ out, int Sq, int Skv,
-                        int n_qtiles, int n_units, int group, float scale_log2, int causal, int *status) {
+                   const __grid_constant__ CUtensorMap tm_v, uint16_t *__restrict__ out, const Problem prob,
+                   float scale_log2, int *status
+                   ) {
   extern __shared__ unsigned char smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   unsigned char *smem = smem_raw + (base - raw);
-  const uint32_t sQ = base;
-  const uint32_t sK0 = base + kQBytes, sV0 = base + kQBytes + 2 * kKVBytes;  // buffer b is at + b * kKVBytes
-  Barriers *bars = reinterpret_cast<Barriers *>(smem + kQBytes + 4 * kKVBytes);
-  volatile int *abort_flag = &bars->abort_flag;
+  const uint32_t sQ = base;                                   // buffer n & 1 of tile n
+  const uint32_t sK = base + 2 * kTileBytes;                  // stage g & 1
+  const uint32_t sV = base + 4 * kTileBytes;
+  Shared *sh = reinterpret_cast<Shared *>(smem + 6 * kTileBytes);
+  volatile int *abort_flag = &sh->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-
-  // tile -> (head, query tile).  Heads are taken in groups of `group`; inside a group the order is tile-major
-  // with the longest causal tiles first, so that the CTAs in flight at any moment belong to few heads (their
-  // K/V stay in L2) while the last CTAs of a group, and of the launch, are the shortest ones.
-  const int per_group = group * n_qtiles;
-  const int grp = blockIdx.x / per_group, rem = blockIdx.x % per_group;
-  const int heads_here = min(group, n_units - grp * group);
-  const int qi = rem / heads_here;
-  const int bh = grp * group + rem % heads_here;
-  const int qt = causal ? (n_qtiles - 1 - qi) : qi;
-  const int kv_off = Skv - Sq;                                    // causal diagonal offset (>= 0)
-  // last kv column any row of the tile sees; Sq and Skv need not be multiples of the tile sizes: rows and
-  // columns past the end of a (batch, head) slice load as zeros (3-D tensor maps), the columns are masked in
-  // the softmax and the rows are not stored
-  const int last_col = causal ? min(Skv - 1, qt * kBM + kv_off + kBM - 1) : Skv - 1;
-  const int nblk = last_col / kBN + 1;
-  const int q_row0 = qt * kBM;                                    // row inside the (batch, head) slice
+  const int G = gridDim.x;
 
   if (threadIdx.x == 0) {
-    bars->abort_flag = 0;
-    bars->skip = (status != nullptr && *reinterpret_cast<volatile int *>(status) != 0) ? 1 : 0;
-    mbar_init(smem_u32(&bars->q_full), 1);
+    sh->abort_flag = 0;
+    sh->skip = (status != nullptr && *reinterpret_cast<volatile int *>(status) != 0) ? 1 : 0;
     for (int b = 0; b < 2; ++b) {
-      mbar_init(smem_u32(&bars->k_full[b]), 1);
-      mbar_init(smem_u32(&bars->k_empty[b]), 1);
-      mbar_init(smem_u32(&bars->v_full[b]), 1);
-      mbar_init(smem_u32(&bars->v_empty[b]), 1);
-      mbar_init(smem_u32(&bars->p_full[b]), 128);
-      mbar_init(smem_u32(&bars->pv_done[b]), 1);
+      mbar_init(smem_u32(&sh->q_full[b]), 1);
+      mbar_init(smem_u32(&sh->q_empty[b]), 1);
+      mbar_init(smem_u32(&sh->k_full[b]), 1);
+      mbar_init(smem_u32(&sh->k_empty[b]), 1);
+      mbar_init(smem_u32(&sh->v_full[b]), 1);
+      mbar_init(smem_u32(&sh->v_empty[b]), 1);
+      mbar_init(smem_u32(&sh->m_ready[b]), 128);
     }
-    mbar_init(smem_u32(&bars->o_full), 1);
-    mbar_init(smem_u32(&bars->s_full), 1);
-    mbar_init(smem_u32(&bars->s_free), 128);
+    for (int b = 0; b < kSBufs; ++b) {
+      mbar_init(smem_u32(&sh->s_full[b]), 1);
+      mbar_init(smem_u32(&sh->p_full[b]), 128);
+      mbar_init(smem_u32(&sh->pv_done[b]), 1);
+    }
+    mbar_init(smem_u32(&sh->o_full), 1);
+    mbar_init(smem_u32(&sh->o_free), 128);
+    mbar_init(smem_u32(&sh->lm_ready), 256);
+    mbar_init(smem_u32(&sh->lm_free), 128);
     fence_barrier_init();
     fence_proxy_async_smem();
   }
   __syncthreads();
-  if (bars->skip) return;  // an earlier CTA of this launch already reported a failure
+  if (sh->skip) return;
 
-  if (warp == 5) {
-    tmem_alloc(smem_u32(&bars->tmem_base), kTmemCols);
+  if (warp == 15) {
+    tmem_alloc(smem_u32(&sh->tmem_base), kTmemCols);
     tmem_relinquish();
   }
-  if (warp == 4 && lane == 0) {
+  if (warp == 12 && lane == 0) {
     tma_prefetch_desc(&tm_q);
     tma_prefetch_desc(&tm_k);
     tma_prefetch_desc(&tm_v);
@@ -136,243 +217,302 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem = bars->tmem_base;
-  const uint32_t tS = tmem, tP0 = tmem + kBN, tO = tmem + 2 * kBN;  // P buffer b is at tP0 + b * kBN / 2 columns
+  const uint32_t tmem = sh->tmem_base;
 
-  const uint32_t b_q_full = smem_u32(&bars->q_full), b_k_full = smem_u32(&bars->k_full[0]),
-                 b_k_empty = smem_u32(&bars->k_empty[0]), b_v_full = smem_u32(&bars->v_full[0]),
-                 b_v_empty = smem_u32(&bars->v_empty[0]), b_s_full = smem_u32(&bars->s_full), b_s_free = smem_u32(&bars->s_free),
-                 b_p_full = smem_u32(&bars->p_full[0]), b_pv_done = smem_u32(&bars->pv_done[0]),
-                 b_o_full = smem_u32(&bars->o_full);  // buffer b of a pair is at +8*b
+  const uint32_t b_q_full = smem_u32(&sh->q_full[0]), b_q_empty = smem_u32(&sh->q_empty[0]),
+                 b_k_full = smem_u32(&sh->k_full[0]), b_k_empty = smem_u32(&sh->k_empty[0]),
+                 b_v_full = smem_u32(&sh->v_full[0]), b_v_empty = smem_u32(&sh->v_empty[0]),
+                 b_s_full = smem_u32(&sh->s_full[0]), b_p_full = smem_u32(&sh->p_full[0]),
+                 b_pv_done = smem_u32(&sh->pv_done[0]), b_o_full = smem_u32(&sh->o_full),
+                 b_o_free = smem_u32(&sh->o_free), b_m_ready = smem_u32(&sh->m_ready[0]),
+                 b_lm_ready = smem_u32(&sh->lm_ready), b_lm_free = smem_u32(&sh->lm_free);  // element i at + 8 * i
 
-  if (warp == 4) {
-    // ================================ TMA producer: Q and K ================================
-    // K and V have a producer thread each: K(j+1) is wanted a whole block before V(j+1), and a single
-    // thread that waits for the V buffer first would hold the K load back.
-    if (lane == 0) {
-      mbar_arrive_expect_tx(b_q_full, kQBytes);
-      tma_load_3d(sQ, &tm_q, 0, q_row0, bh, b_q_full);
-      tma_load_3d(sQ + kQBox, &tm_q, 64, q_row0, bh, b_q_full);
-      int issued = 0;
-      bool ok = true;
-      for (int j = 0; j < nblk && ok; ++j) {
-        const int b = j & 1;
-        ok = mbar_wait(b_k_empty + 8 * b, ((j >> 1) & 1) ^ 1, abort_flag);
-        if (!ok) { report(status, kErrProducer, 2 * j); break; }
-        mbar_arrive_expect_tx(b_k_full + 8 * b, kKVBytes);
-        tma_load_3d(sK0 + b * kKVBytes, &tm_k, 0, j * kBN, bh, b_k_full + 8 * b);
-        tma_load_3d(sK0 + b * kKVBytes + kKVBox, &tm_k, 64, j * kBN, bh, b_k_full + 8 * b);
-        ++issued;
-      }
-      if (!ok) {
-        // Unwinding: let the copies already in flight land before the CTA's shared memory goes away.
-        mbar_wait(b_q_full, 0, abort_flag);
-        for (int spin = 0; spin < 100000; ++spin) {
-          bool done = true;
-          for (int n = 0; n < 2; ++n) {  // the last two loads
-            const int jk = issued - 1 - n;
-            if (jk >= 0) done = done && mbar_try_wait(b_k_full + 8 * (jk & 1), (jk >> 1) & 1);
+  if (warp >= 12) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 80;");
+    if (warp == 12 || warp == 15) {
+      // ================================ TMA producers ================================
+      // warp 12: Q of every tile and the K blocks, in the order the score products want them; warp 15: the V blocks.
+      if (lane == 0) {
+        const bool is_k = warp == 12;
+        const CUtensorMap *tm = is_k ? &tm_k : &tm_v;
+        const uint32_t s_dst = is_k ? sK : sV, b_full = is_k ? b_k_full : b_v_full, b_empty = is_k ? b_k_empty : b_v_empty;
+        bool ok = true;
+        int g = 0, issued = 0, q_issued = 0;
+        for (int i = blockIdx.x, n = 0; i < prob.total && ok; i += G, ++n) {
+          const Tile t = tile_of(prob, i);
+          if (is_k) {
+            ok = mbar_wait(b_q_empty + 8 * (n & 1), ((n >> 1) & 1) ^ 1, abort_flag);
+            if (!ok) { report(status, kErrProducer, -1 - n); break; }
+            mbar_arrive_expect_tx(b_q_full + 8 * (n & 1), kTileBytes);
+            tma_load_3d(sQ + (n & 1) * kTileBytes, &tm_q, 0, t.qt * kBM, t.bh, b_q_full + 8 * (n & 1));
+            tma_load_3d(sQ + (n & 1) * kTileBytes + kBox, &tm_q, 64, t.qt * kBM, t.bh, b_q_full + 8 * (n & 1));
+            ++q_issued;
           }
-          if (done) break;
-          __nanosleep(100);
-        }
-      }
-    }
-    __syncwarp();
-  } else if (warp == 7) {
-    // ================================ TMA producer: V ======================================
-    if (lane == 0) {
-      int issued = 0;
-      bool ok = true;
-      for (int j = 0; j < nblk && ok; ++j) {
-        const int b = j & 1;
-        ok = mbar_wait(b_v_empty + 8 * b, ((j >> 1) & 1) ^ 1, abort_flag);
-        if (!ok) { report(status, kErrProducer, 2 * j + 1); break; }
-        mbar_arrive_expect_tx(b_v_full + 8 * b, kKVBytes);
-        tma_load_3d(sV0 + b * kKVBytes, &tm_v, 0, j * kBN, bh, b_v_full + 8 * b);
-        tma_load_3d(sV0 + b * kKVBytes + kKVBox, &tm_v, 64, j * kBN, bh, b_v_full + 8 * b);
-        ++issued;
-      }
-      if (!ok) {
-        for (int spin = 0; spin < 100000; ++spin) {
-          bool done = true;
-          for (int n = 0; n < 2; ++n) {
-            const int jv = issued - 1 - n;
-            if (jv >= 0) done = done && mbar_try_wait(b_v_full + 8 * (jv & 1), (jv >> 1) & 1);
+          for (int j = 0; j < t.nblk && ok; ++j, ++g) {
+            const int b = g & 1;
+            ok = mbar_wait(b_empty + 8 * b, ((g >> 1) & 1) ^ 1, abort_flag);
+            if (!ok) { report(status, kErrProducer, 2 * g + (is_k ? 0 : 1)); break; }
+            mbar_arrive_expect_tx(b_full + 8 * b, kTileBytes);
+            tma_load_3d(s_dst + b * kTileBytes, tm, 0, j * kBN, t.bh, b_full + 8 * b);
+            tma_load_3d(s_dst + b * kTileBytes + kBox, tm, 64, j * kBN, t.bh, b_full + 8 * b);
+            ++issued;
           }
-          if (done) break;
-          __nanosleep(100);
+        }
+        if (!ok) {
+          // Unwinding: let the copies already in flight land before the CTA's shared memory goes away.
+          for (int spin = 0; spin < 100000; ++spin) {
+            bool done = true;
+            for (int n = 0; n < 2; ++n) {
+              const int jg = issued - 1 - n, jq = q_issued - 1 - n;
+              if (jg >= 0) done = done && mbar_try_wait(b_full + 8 * (jg & 1), (jg >> 1) & 1);
+              if (jq >= 0) done = done && mbar_try_wait(b_q_full + 8 * (jq & 1), (jq >> 1) & 1);
+            }
+            if (done) break;
+            __nanosleep(100);
+          }
         }
       }
+      __syncwarp();
+    } else if (warp == 13) {
+      // ================================ score-product issuer ==================================
+      // A thread of its own for each of the two products: a tcgen05.mma costs its issuing thread 45-60 cycles and a
+      // commit or barrier test 50-150, so one thread for both could not feed the pipe (measured: ~2000 cycles per
+      // block for 16 products).  S(g) goes into the buffer P(g-3) was read from: wait for that PV product first.
+      if (lane == 0) {
+        constexpr int fmt = (DT == NB200_BF16) ? 1 : 0;
+        constexpr uint32_t idesc_qk = umma_idesc_f16(fmt, 0, kBM, kBN);
+        // Descriptors are built once (low words; the high word is common).  K-major operands: 16 elements of the
+        // reduction = 32 bytes inside the 128-byte swizzled row, the two 64-column boxes kBox apart.
+        const uint32_t d_hi = static_cast<uint32_t>(umma_desc_sw128(0, 16, 1024) >> 32);
+        uint32_t dq_lo[kD / 16], dk_lo[kD / 16];   // buffer / stage 1 is kStageStep further
+        constexpr uint32_t kStageStep = kTileBytes >> 4;
+#pragma unroll
+        for (int kk = 0; kk < kD / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * kBox + (kk & 3) * 32;
+          dq_lo[kk] = static_cast<uint32_t>(umma_desc_sw128(sQ + off, 16, 1024));
+          dk_lo[kk] = static_cast<uint32_t>(umma_desc_sw128(sK + off, 16, 1024));
+        }
+        bool ok = true;
+        int g = 0;
+        for (int i = blockIdx.x, n = 0; i < prob.total && ok; i += G, ++n) {
+          const int nblk = tile_of(prob, i).nblk;
+          ok = mbar_wait(b_q_full + 8 * (n & 1), (n >> 1) & 1, abort_flag);
+          if (!ok) { report(status, kErrMma, -1 - n); break; }
+          const uint32_t q_step = (n & 1) * kStageStep;
+          for (int j = 0; j < nblk && ok; ++j, ++g) {
+            const int sb = g % kSBufs;
+            ok = mbar_wait(b_k_full + 8 * (g & 1), (g >> 1) & 1, abort_flag);
+            if (!ok) { report(status, kErrMma, 4 * g); break; }
+            if (g >= kSBufs) {
+              ok = mbar_wait_poll(b_pv_done + 8 * sb, ((g - kSBufs) / kSBufs) & 1, abort_flag);
+              if (!ok) { report(status, kErrMma, 4 * g + 1); break; }
+            }
+            tc_fence_after();
+            const uint32_t d_tmem = tmem + sb * 128, k_step = (g & 1) * kStageStep;
+#pragma unroll
+            for (int kk = 0; kk < kD / 16; ++kk) umma_ss_lo(d_tmem, dq_lo[kk] + q_step, dk_lo[kk] + k_step, d_hi, idesc_qk, kk > 0);
+            umma_commit(b_s_full + 8 * sb);
+            umma_commit(b_k_empty + 8 * (g & 1));
+          }
+          if (ok) umma_commit(b_q_empty + 8 * (n & 1));
+        }
+      }
+      __syncwarp();
+    } else if (warp == 14) {
+      // ================================ PV-product issuer ==================================
+      if (lane == 0) {
+        constexpr int fmt = (DT == NB200_BF16) ? 1 : 0;
+        constexpr uint32_t idesc_pv = umma_idesc_f16(fmt, 1, kBM, kD);
+        // V is MN-major: 16 kv rows = 2 KB, the two 64-column blocks kBox apart
+        const uint32_t d_hi = static_cast<uint32_t>(umma_desc_sw128(0, 16, 1024) >> 32);
+        uint32_t dv_lo[kBN / 16];
+        constexpr uint32_t kStageStep = kTileBytes >> 4;
+#pragma unroll
+        for (int kk = 0; kk < kBN / 16; ++kk) dv_lo[kk] = static_cast<uint32_t>(umma_desc_sw128(sV + kk * 2048, kBox, 1024));
+        bool ok = true;
+        int g = 0;
+        for (int i = blockIdx.x, n = 0; i < prob.total && ok; i += G, ++n) {
+          const int nblk = tile_of(prob, i).nblk;
+          for (int j = 0; j < nblk && ok; ++j, ++g) {
+            const int sb = g % kSBufs;
+            ok = mbar_wait(b_v_full + 8 * (g & 1), (g >> 1) & 1, abort_flag);
+            if (!ok) { report(status, kErrMma, 4 * g + 2); break; }
+            if (j == 0 && n > 0) {   // the epilogue of the previous tile has read O
+              ok = mbar_wait(b_o_free, (n - 1) & 1, abort_flag);
+              if (!ok) { report(status, kErrMma, 4 * g + 3); break; }
+            }
+            ok = mbar_wait_poll(b_p_full + 8 * sb, (g / kSBufs) & 1, abort_flag);
+            if (!ok) { report(status, kErrMma, 4 * g + 3); break; }
+            tc_fence_after();
+            const uint32_t p_tmem = tmem + sb * 128, v_step = (g & 1) * kStageStep;
+#pragma unroll
+            for (int kk = 0; kk < kBN / 16; ++kk)   // P: 16 packed 16-bit values = 8 TMEM columns per product
+              umma_ts_lo(tmem + kTmemO, p_tmem + kk * 8, dv_lo[kk] + v_step, d_hi, idesc_pv, (kk > 0 || j > 0) ? 1u : 0u);
+            umma_commit(b_pv_done + 8 * sb);
+            umma_commit(b_v_empty + 8 * (g & 1));
+            if (j + 1 == nblk) umma_commit(b_o_full);
+          }
+        }
+      }
+      __syncwarp();
     }
-    __syncwarp();
-  } else if (warp == 5) {
-    // ================================ QK issuer ===================================
-    // S = Q K(j)^T.  The softmax warps copy S(j-1) into registers first thing and release the buffer,
-    // so S(j) is computed while they work on block j-1.  A thread of its own, so that the score
-    // products keep flowing while the other issuer waits for the softmax warps.
-    if (lane == 0) {
-      constexpr int fmt = (DT == NB200_BF16) ? 1 : 0;
-      constexpr uint32_t idesc_qk = umma_idesc_f16(fmt, 0, kBM, kBN);
-      // Operand descriptors never change: build them once, so that issuing an MMA is a couple of
-      // instructions (building one per MMA costs ~90 cycles of scalar work and starves the pipe).
-      uint64_t dq[kD / 16], dk[2][kD / 16];
-#pragma unroll
-      for (int kk = 0; kk < kD / 16; ++kk) {
-        // 16 elements of the reduction per MMA = 32 bytes inside the 128-byte swizzled row
-        dq[kk] = umma_desc_sw128(sQ + (kk >> 2) * kQBox + (kk & 3) * 32, 16, 1024);
-#pragma unroll
-        for (int b = 0; b < 2; ++b) dk[b][kk] = umma_desc_sw128(sK0 + b * kKVBytes + (kk >> 2) * kKVBox + (kk & 3) * 32, 16, 1024);
-      }
-      bool ok = mbar_wait(b_q_full, 0, abort_flag);
-      if (!ok) report(status, kErrMma, -1);
-      for (int j = 0; j < nblk && ok; ++j) {
-        const int b = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        ok = mbar_wait(b_k_full + 8 * b, ph, abort_flag);
-        if (!ok) { report(status, kErrMma, 3 * j); break; }
-        if (j >= 1) {
-          ok = mbar_wait(b_s_free, (j - 1) & 1, abort_flag);   // the softmax warps hold S(j-1) in registers
-          if (!ok) { report(status, kErrMma, 3 * j + 1); break; }
-        }
-        tc_fence_after();
-        if (b == 0) {
-#pragma unroll
-          for (int kk = 0; kk < kD / 16; ++kk) umma_ss(tS, dq[kk], dk[0][kk], idesc_qk, kk > 0);
-        } else {
-#pragma unroll
-          for (int kk = 0; kk < kD / 16; ++kk) umma_ss(tS, dq[kk], dk[1][kk], idesc_qk, kk > 0);
-        }
-        umma_commit(b_k_empty + 8 * b);
-        umma_commit(b_s_full);
-      }
-    }
-    __syncwarp();
-  } else if (warp == 6) {
-    // ================================ PV issuer ===================================
-    if (lane == 0) {
-      constexpr int fmt = (DT == NB200_BF16) ? 1 : 0;
-      constexpr uint32_t idesc_pv = umma_idesc_f16(fmt, 1, kBM, kD);
-      uint64_t dv[2][kBN / 16];
-#pragma unroll
-      for (int b = 0; b < 2; ++b)
-#pragma unroll
-        for (int kk = 0; kk < kBN / 16; ++kk)  // V: 16 kv rows = 2 KB; the two 64-column blocks are 8 KB apart
-          dv[b][kk] = umma_desc_sw128(sV0 + b * kKVBytes + kk * 2048, kKVBox, 1024);
-      bool ok = true;
-      for (int j = 0; j < nblk && ok; ++j) {
-        const int b = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        ok = mbar_wait(b_v_full + 8 * b, ph, abort_flag);
-        if (!ok) { report(status, kErrMma, 3 * j + 2); break; }
-        ok = mbar_wait(b_p_full + 8 * b, ph, abort_flag);
-        if (!ok) { report(status, kErrMma, 3 * j + 1); break; }
-        tc_fence_after();
-        // P: 16 packed 16-bit values = 8 TMEM columns per MMA
-        const uint32_t acc0 = j > 0 ? 1u : 0u;
-        if (b == 0) {
-#pragma unroll
-          for (int kk = 0; kk < kBN / 16; ++kk) umma_ts(tO, tP0 + kk * 8, dv[0][kk], idesc_pv, kk > 0 ? 1u : acc0);
-        } else {
-#pragma unroll
-          for (int kk = 0; kk < kBN / 16; ++kk) umma_ts(tO, tP0 + kBN / 2 + kk * 8, dv[1][kk], idesc_pv, kk > 0 ? 1u : acc0);
-        }
-        umma_commit(b_v_empty + 8 * b);
-        umma_commit(b_pv_done + 8 * b);   // P_b is free again, and O holds every product up to block j
-      }
-      if (ok) umma_commit(b_o_full);
-    }
-    __syncwarp();
-  } else {
-    // ================================ softmax + epilogue ==========================
-    const int r = warp * 32 + lane;                         // row in the tile == TMEM lane
-    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
-    float m_used = -INFINITY, l = 0.f;
+  } else if (warp >= 8) {
+    // ================================ epilogue: O / l -> storage dtype -> global ==========================
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
+    const int r = (warp & 3) * 32 + lane;
+    const uint32_t tO = tmem + kTmemO + (static_cast<uint32_t>((warp & 3) * 32) << 16);
     bool ok = true;
-    for (int j = 0; j < nblk; ++j) {
-      const int b = j & 1;
-      // warp-uniform outcome: the TMEM accesses below are warp-collective
-      ok = __all_sync(0xffffffffu, mbar_wait(b_s_full, j & 1, abort_flag));
-      if (!ok) { report(status, kErrSoftmax, j); break; }
+    for (int i = blockIdx.x, n = 0; i < prob.total; i += G, ++n) {
+      const Tile t = tile_of(prob, i);
+      ok = __all_sync(0xffffffffu, mbar_wait(b_lm_ready, n & 1, abort_flag));
+      if (!ok) { report(status, kErrEpilogue, 2 * n); break; }
+      const float m0 = sh->lm[0][r][0], l0 = sh->lm[0][r][1], m1 = sh->lm[1][r][0], l1 = sh->lm[1][r][1];
+      mbar_arrive(b_lm_free);
+      const float mf = fmaxf(m0, m1);   // the running maximum never decreases: the later one is the larger
+      const float l = (l0 > 0.f ? l0 * ex2(m0 - mf) : 0.f) + (l1 > 0.f ? l1 * ex2(m1 - mf) : 0.f);
+      const float inv = 1.f / l;
+      ok = __all_sync(0xffffffffu, mbar_wait(b_o_full, n & 1, abort_flag));
+      if (!ok) { report(status, kErrEpilogue, 2 * n + 1); break; }
       tc_fence_after();
-      const uint32_t tPb = tP0 + b * (kBN / 2) + lane_addr;
-
-      // ---- the 64 scores of this row into registers (one TMEM read); S is then free for block j+1 ----
+      const int q_row = t.qt * kBM + r;
+      uint16_t *dst = out + (static_cast<size_t>(t.bh) * prob.Sq + q_row) * kD;
+      const bool row_exists = q_row < prob.Sq;
+#pragma unroll 1
+      for (int c = 0; c < kD / 32; ++c) {
+        uint32_t o[32];
+        tmem_ld32(tO + c * 32, o);
+        tmem_wait_ld();
+        if (c == kD / 32 - 1) {   // O is in registers: the next tile may overwrite it
+          tc_fence_before();
+          mbar_arrive(b_o_free);
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          uint4 w;
+          w.x = pack2<DT>(__uint_as_float(o[8 * k + 0]) * inv, __uint_as_float(o[8 * k + 1]) * inv);
+          w.y = pack2<DT>(__uint_as_float(o[8 * k + 2]) * inv, __uint_as_float(o[8 * k + 3]) * inv);
+          w.z = pack2<DT>(__uint_as_float(o[8 * k + 4]) * inv, __uint_as_float(o[8 * k + 5]) * inv);
+          w.w = pack2<DT>(__uint_as_float(o[8 * k + 6]) * inv, __uint_as_float(o[8 * k + 7]) * inv);
+          if (row_exists) *reinterpret_cast<uint4 *>(dst + c * 32 + k * 8) = w;
+        }
+      }
+    }
+  } else {
+    // ================================ softmax: warpgroup w takes the blocks g with g & 1 == w ================
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 184;");
+    const int w = warp >> 2;
+    const int r = (warp & 3) * 32 + lane;                     // row in the tile == TMEM lane
+    const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t tO = tmem + kTmemO + lane_addr;
+    const int kv_off = prob.Skv - prob.Sq;
+    int i = blockIdx.x, n = 0, g0 = 0;
+    Tile t = i < prob.total ? tile_of(prob, i) : Tile{0, 0, 0};
+    float m_mine = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int g = w; ok; g += 2) {
+      // tiles that end before block g: hand (maximum, partial sum) to the epilogue and move on
+      while (i < prob.total && g >= g0 + t.nblk) {
+        if (n > 0) {   // the epilogue has read the previous tile's values
+          ok = __all_sync(0xffffffffu, mbar_wait(b_lm_free, (n - 1) & 1, abort_flag));
+          if (!ok) { report(status, kErrSoftmax, -1 - n); break; }
+        }
+        sh->lm[w][r][0] = m_mine;
+        sh->lm[w][r][1] = l;
+        mbar_arrive(b_lm_ready);
+        m_mine = -INFINITY;
+        l = 0.f;
+        g0 += t.nblk;
+        i += G;
+        ++n;
+        if (i < prob.total) t = tile_of(prob, i);
+      }
+      if (!ok || i >= prob.total) break;
+      const int j = g - g0;
+      const int sb = g % kSBufs;
+      const uint32_t tS = tmem + sb * 128 + lane_addr;
+      ok = __all_sync(0xffffffffu, mbar_wait(b_s_full + 8 * sb, (g / kSBufs) & 1, abort_flag));
+      if (!ok) { report(status, kErrSoftmax, g); break; }
+      tc_fence_after();
+      float m_prev = 0.f;
+      if (g > 0) {
+        // block g-1 has decided on its maximum (and, before that, has read the slot this block will overwrite)
+        ok = __all_sync(0xffffffffu, mbar_wait(b_m_ready + 8 * ((g - 1) & 1), ((g - 1) >> 1) & 1, abort_flag));
+        if (!ok) { report(status, kErrSoftmax, 1000 + g); break; }
+        if (j > 0) m_prev = sh->mslot[(g - 1) & 1][r];
+      }
       uint32_t v[kBN];
-      tmem_ld32p(tS + lane_addr, v);
-      tmem_ld32p(tS + lane_addr + 32, v + 32);
+      tmem_ld32p(tS, v);
+      tmem_ld32p(tS + 32, v + 32);
+      tmem_ld32p(tS + 64, v + 64);
+      tmem_ld32p(tS + 96, v + 96);
       tmem_wait_ld();
-      tc_fence_before();
-      mbar_arrive(b_s_free);
-      // column c of block j exists iff j*64 + c < Skv and, if causal, is visible to row r iff j*64 + c <= qt*128 + kv_off + r
-      const int vis = min(causal ? (qt * kBM + kv_off + r - j * kBN) : kBN, Skv - 1 - j * kBN);  // columns 0..vis are visible
+      // column c of block j exists iff j*128 + c < Skv and, if causal, row r sees it iff j*128 + c <= qt*128 + kv_off + r
+      const int vis = min(prob.causal ? (t.qt * kBM + kv_off + r - j * kBN) : kBN, prob.Skv - 1 - j * kBN);
       if (vis < kBN - 1) {
 #pragma unroll
-        for (int i = 0; i < kBN; ++i) v[i] = (i > vis) ? 0xff800000u : v[i];  // -inf: 2^(-inf) = 0
+        for (int c = 0; c < kBN; ++c) v[c] = (c > vis) ? 0xff800000u : v[c];
       }
-
-      // ---- row maximum (four chains of three-input maxima) ----
-      float mc[4];
+      // ---- row maximum: eight chains of three-input maxima ----
+      float mc[8];
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
+      for (int c = 0; c < 8; ++c)
         mc[c] = max3(__uint_as_float(v[c * 16]), __uint_as_float(v[c * 16 + 1]), __uint_as_float(v[c * 16 + 2]));
 #pragma unroll
-      for (int i = 3; i + 1 < 16; i += 2) {
+      for (int k = 3; k + 1 < 16; k += 2) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
-          mc[c] = max3(mc[c], __uint_as_float(v[c * 16 + i]), __uint_as_float(v[c * 16 + i + 1]));
+        for (int c = 0; c < 8; ++c)
+          mc[c] = max3(mc[c], __uint_as_float(v[c * 16 + k]), __uint_as_float(v[c * 16 + k + 1]));
       }
 #pragma unroll
-      for (int c = 0; c < 4; ++c) mc[c] = fmaxf(mc[c], __uint_as_float(v[c * 16 + 15]));
-      const float mx = fmaxf(max3(mc[0], mc[1], mc[2]), mc[3]);
-      const float m_blk = mx * scale_log2;                   // scale_log2 > 0; -inf if the whole row is masked
-      if (j == 0) {
-        m_used = m_blk;                                      // block 0 always has a visible column
-      } else {
-        const bool need = m_blk > m_used + kRescaleThreshold;
-        if (__any_sync(0xffffffffu, need)) {
-          // O must hold every product up to block j-1 and none may be in flight: wait for PV(j-1)
-          // (the products before it were issued earlier by the same thread and complete in order).
-          ok = __all_sync(0xffffffffu, mbar_wait(b_pv_done + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1, abort_flag));
-          if (!ok) { report(status, kErrSoftmax, 1000 + j); break; }
-          tc_fence_after();
-          const float f = need ? ex2(m_used - m_blk) : 1.f;
-          if (need) m_used = m_blk;
-          l *= f;
-#pragma unroll 1
-          for (int c = 0; c < kD / 16; ++c) {  // 16 columns at a time: the scores stay live in registers
-            uint32_t o[16];
-            tmem_ld16(tO + lane_addr + c * 16, o);
-            tmem_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
-            tmem_st16(tO + lane_addr + c * 16, o);
-          }
-          tmem_wait_st();
-        }
+      for (int c = 0; c < 8; ++c) mc[c] = fmaxf(mc[c], __uint_as_float(v[c * 16 + 15]));
+      const float mx = fmaxf(max3(mc[0], mc[1], mc[2]), fmaxf(max3(mc[3], mc[4], mc[5]), fmaxf(mc[6], mc[7])));
+      const float m_blk = mx * scale_log2;                     // -inf if the whole row is masked in this block
+      // ---- the maximum to use: the one block g-1 decided on, unless this block exceeds it by more than 2^8 ----
+      float m_new = m_blk;                                     // block 0 of a tile always has a visible column
+      bool need = false;
+      if (j > 0) {
+        need = m_blk > m_prev + kRescaleThreshold;
+        m_new = need ? m_blk : m_prev;
       }
-
-      // ---- p = 2^(s*scale - m) on packed pairs, row sum, pack to 16 bit, write P_b ----
-      if (j >= 2) {  // PV(j-2) read P_b; it completed long ago, this only makes the order formal
-        ok = __all_sync(0xffffffffu, mbar_wait(b_pv_done + 8 * b, ((j - 2) >> 1) & 1, abort_flag));
-        if (!ok) { report(status, kErrSoftmax, 2000 + j); break; }
+      sh->mslot[g & 1][r] = m_new;
+      mbar_arrive(b_m_ready + 8 * (g & 1));
+      if (__any_sync(0xffffffffu, need)) {
+        // O must hold every product up to block g-1 and none may be in flight
+        ok = __all_sync(0xffffffffu, mbar_wait(b_pv_done + 8 * ((g - 1) % kSBufs), ((g - 1) / kSBufs) & 1, abort_flag));
+        if (!ok) { report(status, kErrSoftmax, 2000 + g); break; }
         tc_fence_after();
+        const float f = need ? ex2(m_prev - m_blk) : 1.f;
+#pragma unroll 1
+        for (int c = 0; c < kD / 16; ++c) {
+          uint32_t o[16];
+          tmem_ld16(tO + c * 16, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int k = 0; k < 16; ++k) o[k] = __float_as_uint(__uint_as_float(o[k]) * f);
+          tmem_st16(tO + c * 16, o);
+        }
+        tmem_wait_st();
       }
-      const uint64_t c2 = f2_pack(scale_log2, scale_log2), nm2 = f2_pack(-m_used, -m_used);
+      if (m_mine != m_new) {   // bring the partial sum to the new maximum (2^(-inf) = 0 on the first block)
+        l *= ex2(m_mine - m_new);
+        m_mine = m_new;
+      }
+      // ---- p = 2^(s*scale - m), row sum, pack to 16 bit; P overwrites columns 0..63 of S ----
+      const uint64_t c2 = f2_pack(scale_log2, scale_log2), nm2 = f2_pack(-m_new, -m_new);
       uint64_t lsum2 = f2_pack(0.f, 0.f);
 #pragma unroll
       for (int c = 0; c < kBN / 32; ++c) {
         uint32_t pk[16];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
+        for (int k = 0; k < 16; ++k) {
           const uint64_t x2 = f2_fma(
-              f2_pack(__uint_as_float(v[c * 32 + 2 * i]), __uint_as_float(v[c * 32 + 2 * i + 1])), c2, nm2);
+              f2_pack(__uint_as_float(v[c * 32 + 2 * k]), __uint_as_float(v[c * 32 + 2 * k + 1])), c2, nm2);
           const float2 x = f2_unpack(x2);
           const float p0 = ex2(x.x), p1 = ex2(x.y);
           lsum2 = f2_add(lsum2, f2_pack(p0, p1));
-          pk[i] = pack2<DT>(p0, p1);
+          pk[k] = pack2<DT>(p0, p1);
         }
-        tmem_st16(tPb + c * 16, pk);
+        tmem_st16(tS + c * 16, pk);
       }
       {
         const float2 ls = f2_unpack(lsum2);
@@ -380,47 +520,19 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
       }
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(b_p_full + 8 * b);
-    }
-
-    // ---- epilogue: O / l -> storage dtype -> global ----
-    if (ok) {
-      ok = __all_sync(0xffffffffu, mbar_wait(b_o_full, 0, abort_flag));
-      if (!ok) report(status, kErrEpilogue, 0);
-    }
-    if (ok) {
-      tc_fence_after();
-      const float inv = 1.f / l;
-      uint16_t *dst = out + (static_cast<size_t>(bh) * Sq + q_row0 + r) * kD;
-      const bool row_exists = q_row0 + r < Sq;   // the last tile of a slice may be partial
-#pragma unroll 1
-      for (int c = 0; c < kD / 32; ++c) {
-        uint32_t o[32];
-        tmem_ld32(tO + lane_addr + c * 32, o);
-        tmem_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          uint4 w;
-          w.x = pack2<DT>(__uint_as_float(o[8 * i + 0]) * inv, __uint_as_float(o[8 * i + 1]) * inv);
-          w.y = pack2<DT>(__uint_as_float(o[8 * i + 2]) * inv, __uint_as_float(o[8 * i + 3]) * inv);
-          w.z = pack2<DT>(__uint_as_float(o[8 * i + 4]) * inv, __uint_as_float(o[8 * i + 5]) * inv);
-          w.w = pack2<DT>(__uint_as_float(o[8 * i + 6]) * inv, __uint_as_float(o[8 * i + 7]) * inv);
-          if (row_exists) *reinterpret_cast<uint4 *>(dst + c * 32 + i * 8) = w;
-        }
-      }
+      mbar_arrive(b_p_full + 8 * sb);
     }
   }
 
   // ================================ tear-down =====================================
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 15) {
     tc_fence_after();
     tmem_dealloc(tmem, kTmemCols);
   }
 }
 
-// cuTensorMapEncodeTiled, resolved through the runtime so that the library does not link libcuda.
 using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                    const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
                                    CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
@@ -438,7 +550,6 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
-// [slices, rows, 128] 16-bit row-major tensor, boxes of 1 slice x box_rows rows x 64 columns, 128-byte swizzle.
 int make_tile_map(CUtensorMap *tm, const void *ptr, long long slices, long long rows, int dtype, int box_rows) {
   EncodeTiledFn enc = encode_tiled_fn();
   NB200_REQUIRE(enc, NB200_ERR_LAUNCH, "attn_fwd: cuTensorMapEncodeTiled is not available from the driver");
@@ -457,16 +568,22 @@ int make_tile_map(CUtensorMap *tm, const void *ptr, long long slices, long long 
 template <int DT>
 int launch_tc(const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv, void *out, int BH, int Sq,
               int Skv, float scale_log2, int causal, int *status, cudaStream_t st) {
-  // per-device attribute: set on every call so that any current device is covered
-  NB200_CHECK_CUDA(cudaFuncSetAttribute(attn_fwd_tcgen05_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        kSmemBytes));
-  // two CTAs of ~97 KB must fit: ask for the largest shared-memory carve-out
-  NB200_CHECK_CUDA(cudaFuncSetAttribute(attn_fwd_tcgen05_kernel<DT>, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                        cudaSharedmemCarveoutMaxShared));
-  const int n_qtiles = (Sq + kBM - 1) / kBM;
-  const int group = min(BH, kHeadGroup);
-  attn_fwd_tcgen05_kernel<DT><<<dim3(BH * n_qtiles), dim3(kThreads), kSmemBytes, st>>>(
-      tq, tk, tv, static_cast<uint16_t *>(out), Sq, Skv, n_qtiles, BH, group, scale_log2, causal, status);
+  NB200_CHECK_CUDA(cudaFuncSetAttribute(attn_fwd_tcgen05_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+  int dev = 0, sms = 0;
+  NB200_CHECK_CUDA(cudaGetDevice(&dev));
+  NB200_CHECK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  Problem p;
+  p.Sq = Sq;
+  p.Skv = Skv;
+  p.n_qtiles = (Sq + kBM - 1) / kBM;
+  p.n_units = BH;
+  p.group = min(BH, kHeadGroup);
+  p.causal = causal;
+  p.total = BH * p.n_qtiles;
+  const int grid = min(p.total, sms);
+  attn_fwd_tcgen05_kernel<DT><<<dim3(grid), dim3(kThreads), kSmemBytes, st>>>(tq, tk, tv, static_cast<uint16_t *>(out), p,
+                                                                        scale_log2, status
+  );
   NB200_CHECK_CUDA(cudaGetLastError());
   return NB200_OK;
 }
