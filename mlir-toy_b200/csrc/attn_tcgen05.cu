@@ -1,7 +1,9 @@
 // Fused attention forward on Blackwell tensor cores: persistent CTAs, KV blocks of 128 rows, two softmax
 // warpgroups taking alternate blocks (f16 / bf16 storage, D = 128).
 //
-// A CTA (one per SM) works through a list of tiles of 128 query rows.  The KV sequence of a tile is walked in blocks
+// A CTA (one per SM) works through tiles of 128 query rows, taken one at a time from a global counter in launch
+// order (heads in groups, longest causal tiles first), so that all CTAs end within one short tile of each other.
+// The KV sequence of a tile is walked in blocks
 // of 128 rows; the blocks of all the CTA's tiles form one stream, numbered g = 0, 1, 2, ...:
 //
 //   S(g) = Q K(g)^T      8 x tcgen05.mma 128x128x16, both operands in shared memory, into TMEM buffer g % 3
@@ -36,6 +38,8 @@
 // Every wait is bounded; on expiry the CTA records a code in the status words and unwinds.
 #include <cuda.h>
 
+#include <atomic>
+
 #include "nb200_common.cuh"
 #include "sm100_primitives.cuh"
 
@@ -55,6 +59,7 @@ constexpr int kSBufs = 3;
 constexpr int kTmemCols = 512;                  // S/P 0 | S/P 1 | S/P 2 | O, 128 columns each
 constexpr int kTmemO = 384;
 constexpr float kRescaleThreshold = 8.0f;
+constexpr int kSched = 16;                      // ring of tile indices handed from the scheduling thread to the other roles
 
 enum : int { kErrProducer = 1, kErrMma = 2, kErrSoftmax = 3, kErrEpilogue = 4 };
 
@@ -62,6 +67,8 @@ struct Shared {
   uint64_t q_full[2], q_empty[2], k_full[2], k_empty[2], v_full[2], v_empty[2];
   uint64_t s_full[kSBufs], p_full[kSBufs], pv_done[kSBufs];
   uint64_t o_full, o_free, m_ready[2], lm_ready, lm_free;
+  uint64_t sched_full[kSched];
+  int tile_slot[kSched];
   uint32_t tmem_base;
   int abort_flag;
   int skip;
@@ -163,7 +170,7 @@ template <int DT>
 __global__ void __launch_bounds__(kThreads, 1)
 attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                    const __grid_constant__ CUtensorMap tm_v, uint16_t *__restrict__ out, const Problem prob,
-                   float scale_log2, int *status
+                   float scale_log2, unsigned int *tile_counter, int *status
                    ) {
   extern __shared__ unsigned char smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -199,6 +206,7 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
     mbar_init(smem_u32(&sh->o_free), 128);
     mbar_init(smem_u32(&sh->lm_ready), 256);
     mbar_init(smem_u32(&sh->lm_free), 128);
+    for (int b = 0; b < kSched; ++b) mbar_init(smem_u32(&sh->sched_full[b]), 1);
     fence_barrier_init();
     fence_proxy_async_smem();
   }
@@ -225,7 +233,19 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
                  b_s_full = smem_u32(&sh->s_full[0]), b_p_full = smem_u32(&sh->p_full[0]),
                  b_pv_done = smem_u32(&sh->pv_done[0]), b_o_full = smem_u32(&sh->o_full),
                  b_o_free = smem_u32(&sh->o_free), b_m_ready = smem_u32(&sh->m_ready[0]),
-                 b_lm_ready = smem_u32(&sh->lm_ready), b_lm_free = smem_u32(&sh->lm_free);  // element i at + 8 * i
+                 b_lm_ready = smem_u32(&sh->lm_ready), b_lm_free = smem_u32(&sh->lm_free),
+                 b_sched = smem_u32(&sh->sched_full[0]);  // element i at + 8 * i
+
+  // Tiles are dealt dynamically: the K producer takes the CTA's n-th tile from a global counter (the first one is
+  // the CTA's own index, so nothing waits at the start) and posts it in a ring; every other role reads it there.
+  // With the longest tiles first this keeps the CTAs within one short tile of each other at the end, where a fixed
+  // round-robin deal left 4 % (256 heads) to 15 % (32 heads) of imbalance.  The roles are never more than 7 tiles
+  // apart (2 Q buffers, 3 score buffers, one O), so 16 slots need no "empty" barrier.  A value >= total ends the list;
+  // -1 is an expired wait.
+  auto tile_at = [&](int n) -> int {
+    if (!mbar_wait(b_sched + 8 * (n % kSched), (n / kSched) & 1, abort_flag)) return -1;
+    return *reinterpret_cast<volatile int *>(&sh->tile_slot[n % kSched]);
+  };
 
   if (warp >= 12) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 80;");
@@ -238,7 +258,17 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         const uint32_t s_dst = is_k ? sK : sV, b_full = is_k ? b_k_full : b_v_full, b_empty = is_k ? b_k_empty : b_v_empty;
         bool ok = true;
         int g = 0, issued = 0, q_issued = 0;
-        for (int i = blockIdx.x, n = 0; i < prob.total && ok; i += G, ++n) {
+        for (int n = 0; ok; ++n) {
+          int i;
+          if (is_k) {   // this thread is the scheduler
+            i = n == 0 ? static_cast<int>(blockIdx.x) : G + static_cast<int>(atomicAdd(tile_counter, 1u));
+            sh->tile_slot[n % kSched] = i;
+            mbar_arrive(b_sched + 8 * (n % kSched));
+          } else {
+            i = tile_at(n);
+            if (i < 0) { report(status, kErrProducer, -1000 - n); ok = false; break; }
+          }
+          if (i >= prob.total) break;
           const Tile t = tile_of(prob, i);
           if (is_k) {
             ok = mbar_wait(b_q_empty + 8 * (n & 1), ((n >> 1) & 1) ^ 1, abort_flag);
@@ -294,7 +324,10 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         }
         bool ok = true;
         int g = 0;
-        for (int i = blockIdx.x, n = 0; i < prob.total && ok; i += G, ++n) {
+        for (int n = 0; ok; ++n) {
+          const int i = tile_at(n);
+          if (i < 0) { report(status, kErrMma, -1000 - n); break; }
+          if (i >= prob.total) break;
           const int nblk = tile_of(prob, i).nblk;
           ok = mbar_wait(b_q_full + 8 * (n & 1), (n >> 1) & 1, abort_flag);
           if (!ok) { report(status, kErrMma, -1 - n); break; }
@@ -331,7 +364,10 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         for (int kk = 0; kk < kBN / 16; ++kk) dv_lo[kk] = static_cast<uint32_t>(umma_desc_sw128(sV + kk * 2048, kBox, 1024));
         bool ok = true;
         int g = 0;
-        for (int i = blockIdx.x, n = 0; i < prob.total && ok; i += G, ++n) {
+        for (int n = 0; ok; ++n) {
+          const int i = tile_at(n);
+          if (i < 0) { report(status, kErrMma, -1000 - n); break; }
+          if (i >= prob.total) break;
           const int nblk = tile_of(prob, i).nblk;
           for (int j = 0; j < nblk && ok; ++j, ++g) {
             const int sb = g % kSBufs;
@@ -362,7 +398,10 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
     const int r = (warp & 3) * 32 + lane;
     const uint32_t tO = tmem + kTmemO + (static_cast<uint32_t>((warp & 3) * 32) << 16);
     bool ok = true;
-    for (int i = blockIdx.x, n = 0; i < prob.total; i += G, ++n) {
+    for (int n = 0;; ++n) {
+      const int i = __shfl_sync(0xffffffffu, tile_at(n), 0);
+      if (i < 0) { report(status, kErrEpilogue, -1000 - n); break; }
+      if (i >= prob.total) break;
       const Tile t = tile_of(prob, i);
       ok = __all_sync(0xffffffffu, mbar_wait(b_lm_ready, n & 1, abort_flag));
       if (!ok) { report(status, kErrEpilogue, 2 * n); break; }
@@ -405,10 +444,12 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t tO = tmem + kTmemO + lane_addr;
     const int kv_off = prob.Skv - prob.Sq;
-    int i = blockIdx.x, n = 0, g0 = 0;
-    Tile t = i < prob.total ? tile_of(prob, i) : Tile{0, 0, 0};
+    int n = 0, g0 = 0;
+    int i = __shfl_sync(0xffffffffu, tile_at(0), 0);
+    bool ok = i >= 0;
+    if (!ok) report(status, kErrSoftmax, -1000);
+    Tile t = (ok && i < prob.total) ? tile_of(prob, i) : Tile{0, 0, 0};
     float m_mine = -INFINITY, l = 0.f;
-    bool ok = true;
     for (int g = w; ok; g += 2) {
       // tiles that end before block g: hand (maximum, partial sum) to the epilogue and move on
       while (i < prob.total && g >= g0 + t.nblk) {
@@ -422,8 +463,9 @@ attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         m_mine = -INFINITY;
         l = 0.f;
         g0 += t.nblk;
-        i += G;
         ++n;
+        i = __shfl_sync(0xffffffffu, tile_at(n), 0);
+        if (i < 0) { report(status, kErrSoftmax, -1000 - n); ok = false; break; }
         if (i < prob.total) t = tile_of(prob, i);
       }
       if (!ok || i >= prob.total) break;
@@ -565,6 +607,9 @@ int make_tile_map(CUtensorMap *tm, const void *ptr, long long slices, long long 
   return NB200_OK;
 }
 
+// Tile counters of the launches in flight: a launch takes the next slot and zeroes it on its stream before the kernel.
+__device__ unsigned int g_tile_counters[64];
+
 template <int DT>
 int launch_tc(const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv, void *out, int BH, int Sq,
               int Skv, float scale_log2, int causal, int *status, cudaStream_t st) {
@@ -581,8 +626,13 @@ int launch_tc(const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &t
   p.causal = causal;
   p.total = BH * p.n_qtiles;
   const int grid = min(p.total, sms);
+  static std::atomic<unsigned> next_slot{0};
+  unsigned int *counters = nullptr;
+  NB200_CHECK_CUDA(cudaGetSymbolAddress(reinterpret_cast<void **>(&counters), g_tile_counters));
+  unsigned int *counter = counters + (next_slot.fetch_add(1) & 63u);
+  NB200_CHECK_CUDA(cudaMemsetAsync(counter, 0, sizeof(unsigned int), st));
   attn_fwd_tcgen05_kernel<DT><<<dim3(grid), dim3(kThreads), kSmemBytes, st>>>(tq, tk, tv, static_cast<uint16_t *>(out), p,
-                                                                        scale_log2, status
+                                                                        scale_log2, counter, status
   );
   NB200_CHECK_CUDA(cudaGetLastError());
   return NB200_OK;
