@@ -62,7 +62,9 @@ const char *nb200_last_error(void);
  * f16 / bf16 with D == 128 (any Sq, Skv) and 16-byte aligned tensors run on tcgen05 tensor cores with
  * TMA-staged tiles (misaligned tensors are NB200_ERR_BAD_ARG, not a fall-back); f32, and f16 / bf16 with another
  * D, run on an exact-fp32 SIMT kernel, which needs D a multiple of 32, D <= 256 and B * H <= 65535 and returns
- * NB200_ERR_UNSUPPORTED otherwise.
+ * NB200_ERR_UNSUPPORTED otherwise.  The tensor-core path is a persistent kernel whose CTAs take tiles from a
+ * counter inside the library: the call enqueues a 4-byte memset of that counter on `stream` in front of the kernel
+ * (capturable in a CUDA graph); up to 64 such launches may be in flight on one GPU at a time.
  */
 int nb200_attn_fwd(const void *q, const void *k, const void *v, void *out,
                    int B, int H, int Sq, int Skv, int D, int dtype,

@@ -160,6 +160,22 @@ def test_lengths_that_are_not_multiples_of_the_tiles(cuda, native_lib, Sq, Skv, 
         assert_storage_close(out[:, h:h + 1], ref, BF16_ATOL)
 
 
+@pytest.mark.parametrize("Sq,Skv,causal", [(128, 128, True), (200, 200, True), (128, 300, False), (384, 384, True)])
+def test_more_short_tiles_than_sms(cuda, native_lib, Sq, Skv, causal):
+    """Hundreds of tiles of one to three KV blocks each: the persistent CTAs take tile after tile from the global
+    counter, and the roles of a CTA run several tiles apart.  Every element against the oracle."""
+    from neptune_mlir import runtime
+
+    B, H, D = 2, 150, 128
+    q, k, v = inputs.attention_inputs(B, H, Sq, D, torch.bfloat16, config=61, Skv=Skv)
+    out = torch.full((B, H, Sq, D), float("nan"), dtype=torch.bfloat16, device=cuda)
+    for _ in range(2):   # the second launch takes another tile counter
+        runtime.attn_fwd(q.to(cuda), k.to(cuda), v.to(cuda), out, shape=(B, H, Sq, D), kv_len=Skv, dtype="bf16",
+                         scale_log2=attention.scale_log2(D), causal=causal)
+    finish()
+    assert_storage_close(out, attention.attention_reference(q, k, v, causal=causal), BF16_ATOL)
+
+
 def test_config2_full_size_sampled(cuda, native_lib):
     """B=8, H=32, S=4096, D=128 bf16 causal; sampled (batch, head, row block) tiles against the oracle."""
     B, H, S, D = 8, 32, 4096, 128

@@ -56,3 +56,40 @@ def test_decode_step_replays_from_a_cuda_graph(cuda, native_lib):
         graph.replay()
         finish()
         assert_storage_close(out, decode.decode_reference(q, k, v), 2e-2)
+
+
+def test_attention_replays_from_a_cuda_graph(cuda, native_lib):
+    """The attention launch is a 4-byte memset of its tile counter plus one kernel, both on the current stream:
+    it can be captured once and replayed on new inputs (more tiles than SMs, so the dynamic deal is exercised)."""
+    from neptune_mlir import torch_ops  # noqa: F401
+
+    B, H, S, D = 1, 6, 4096, 128
+    scale = 1.0 / math.sqrt(D)
+    qd = torch.empty((B, H, S, D), dtype=torch.bfloat16, device=cuda)
+    kd, vd, out = torch.empty_like(qd), torch.empty_like(qd), torch.empty_like(qd)
+
+    def load(cfg):
+        q, k, v = inputs.attention_inputs(B, H, S, D, torch.bfloat16, config=cfg)
+        qd.copy_(q)
+        kd.copy_(k)
+        vd.copy_(v)
+        return q, k, v
+
+    load(41)
+    side = torch.cuda.Stream(device=cuda)
+    side.wait_stream(torch.cuda.current_stream(cuda))
+    with torch.cuda.stream(side):
+        torch.ops.nb200.attn_fwd(qd, kd, vd, out, scale, True)
+    torch.cuda.current_stream(cuda).wait_stream(side)
+    finish()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        torch.ops.nb200.attn_fwd(qd, kd, vd, out, scale, True)
+    for cfg in (42, 43):
+        q, k, v = load(cfg)
+        out.fill_(float("nan"))
+        graph.replay()
+        finish()
+        ref = attention.attention_reference(q[:, :2], k[:, :2], v[:, :2], causal=True)
+        assert_storage_close(out[:, :2], ref, 2e-2)
+        assert torch.isfinite(out.float()).all()
