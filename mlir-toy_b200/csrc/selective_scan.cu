@@ -50,6 +50,11 @@ __device__ __forceinline__ void cp_async16(void *smem_dst, const void *gsrc) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gsrc) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ float tanh_approx(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 template <int N> __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
@@ -220,7 +225,8 @@ selective_scan_kernel(const uint16_t *__restrict__ u, const uint16_t *__restrict
 #pragma unroll
       for (int i = 0; i < TS; ++i) {
         const float yv = fmaf(dskip, uu4[i], y8[i]);
-        o4[i] = yv * zz4[i] * __frcp_rn(1.f + ex2(-zz4[i] * kLog2e));
+        // silu(z) = z * sigmoid(z) = z * (0.5 + 0.5 tanh(z / 2)): one special-function result instead of two
+        o4[i] = yv * zz4[i] * fmaf(0.5f, tanh_approx(0.5f * zz4[i]), 0.5f);
       }
       if constexpr (TS == 4) {
         *reinterpret_cast<uint2 *>(sm.out + off) = make_uint2(pack2<DT>(o4[0], o4[1]), pack2<DT>(o4[2], o4[3]));
