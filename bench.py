@@ -64,11 +64,12 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # full-size workload read and wrote 250.8 MB (dram__bytes_read.sum + dram__bytes_write.sum); the traffic grows in
 # proportion to the unit count because K/V of a head stay in L2 while its tiles run.  The compulsory traffic is
 # 4 * S * D * 2 bytes per unit = 4.19 MB; the capture is 6.5 % below it (part of Q/K/V was still in L2 from the fill).
-ATTN_DRAM_TRAFFIC_BYTES_PER_UNIT = 250_811_136 / 64
+ATTN_DRAM_TRAFFIC_BYTES_PER_UNIT = 256_879_872 / 64
 
 # Warp instructions per state update of the selective-scan kernel (8 states per thread), from a profiler count of
-# smsp__inst_executed.sum over a launch of known size: 203.5 M instructions for 4 * 4096 * 4096 * 16 updates.
-SCAN_WARP_INSTR_PER_UPDATE = 203.5e6 / (4 * 4096 * 4096 * 16)
+# smsp__inst_executed.sum over one launch of the full configuration: 382.9 M instructions for 8 * 4096 * 4096 * 16
+# updates (45.6 per warp and time step).
+SCAN_WARP_INSTR_PER_UPDATE = 382.857e6 / (8 * 4096 * 4096 * 16)
 
 LOG2E = math.log2(math.e)
 BF16_ATOL = 2e-2
@@ -635,9 +636,9 @@ def bench_extra(args, d: Dist, dev, flush, pk, pk_kind) -> dict:
         total = 4 * c["B"] * c["Dm"] * c["L"] * 2 + 2 * c["B"] * c["N"] * c["L"] * 2 + c["Dm"] * c["N"] * 4 + c["Dm"] * 4
         updates = c["B"] * c["Dm"] * c["L"] * c["N"]
         clk = (clocks.summary()["sm_mhz"] or pk.get("sm_max_mhz", 1965.0)) * 1e6
-        # two more floors of this kernel, per GPU: one ex2 per state update (plus two special-function results per
+        # two more floors of this kernel, per GPU: one ex2 per state update (plus one special-function result per
         # output element for the gate) at 16 results per clock per SM; and the issue slots, 4 per clock per SM
-        mufu_s = (updates + 2 * c["B"] * c["Dm"] * c["L"]) / d.world / (16 * sm_count * clk)
+        mufu_s = (updates + c["B"] * c["Dm"] * c["L"]) / d.world / (16 * sm_count * clk)
         issue_s = updates * SCAN_WARP_INSTR_PER_UPDATE / d.world / (4 * sm_count * clk)
         entry = record("selective_scan", ms, total, {
             "config": "B=8 D=4096 L=4096 N=16 (configs[3])", "launches_per_step": 1,

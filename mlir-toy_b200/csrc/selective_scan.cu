@@ -19,6 +19,8 @@
 //     time steps), which leaves each lane four adjacent time steps, for which it applies the skip
 //     term and the SiLU gate and writes two packed pairs into the output tile, stored to global
 //     memory as full rows.
+#include <cstdlib>
+
 #include "nb200_common.cuh"
 
 namespace nb200 {
@@ -258,9 +260,14 @@ void launch_scan(const void *u, const void *delta, const float *A, const void *B
 }
 
 // States per thread for a problem of `ctas` CTAs on a GPU of `sms` SMs.  Measured on 148 SMs (D = 4096, L = 4096,
-// time in ms for 8 / 4 / 2 states per thread): 1024 CTAs 0.80 / 0.84 / -, 512 CTAs 0.48 / 0.48 / 0.61,
+// time in ms for 8 / 4 / 2 states per thread, before the gate went to tanh.approx; after it 1024 CTAs take
+// 0.71 / 0.79): 1024 CTAs 0.80 / 0.84 / -, 512 CTAs 0.48 / 0.48 / 0.61,
 // 256 CTAs 0.37 / 0.29 / 0.31, 128 CTAs 0.35 / 0.22 / 0.21.
 int states_per_thread(long long ctas, int sms) {
+  if (const char *e = getenv("NB200_SCAN_STATES")) {   // 8, 4 or 2: forces the choice (tests and tuning)
+    const int v = atoi(e);
+    if (v == 8 || v == 4 || v == 2) return v;
+  }
   const long long want = 3ll * 4 * sms;   // about three warps of 8 states per scheduler
   if (ctas * 2 >= want) return 8;
   if (ctas * 8 >= want) return 4;
