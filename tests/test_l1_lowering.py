@@ -1,6 +1,7 @@
 """Level-1 (scheduled tile IR) -> HTile lowering (neptune_mlir.l1)."""
 
 import ast
+import os
 from collections import Counter
 from pathlib import Path
 
@@ -9,7 +10,8 @@ import pytest
 from neptune_mlir import htile_native, htile_text, l1, passes, programs
 from neptune_mlir.translators import b200
 
-REFERENCE_ROOT = Path("/root/reference")
+# the reference project's tree, when it is available ($NEPTUNE_REFERENCE_ROOT, else a sibling "reference" directory)
+REFERENCE_ROOT = Path(os.environ.get("NEPTUNE_REFERENCE_ROOT", Path(__file__).resolve().parents[2] / "reference"))
 REFERENCE_L1 = REFERENCE_ROOT / "tests" / "data" / "flash_attention_l1.mlir"
 REFERENCE_HTILE = REFERENCE_ROOT / "tests" / "data" / "flash_attention_htile.mlir"
 
