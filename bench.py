@@ -63,8 +63,8 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # DRAM bytes per launch of the attention kernel, per (batch, head) unit: a profiler capture of 64 units of the
 # full-size workload read and wrote 250.8 MB (dram__bytes_read.sum + dram__bytes_write.sum); the traffic grows in
 # proportion to the unit count because K/V of a head stay in L2 while its tiles run.  The compulsory traffic is
-# 4 * S * D * 2 bytes per unit = 4.19 MB; the capture is 6.5 % below it (part of Q/K/V was still in L2 from the fill).
-ATTN_DRAM_TRAFFIC_BYTES_PER_UNIT = 256_879_872 / 64
+# 4 * S * D * 2 bytes per unit = 4.19 MB; the capture is 7.4 % below it (part of Q/K/V was still in L2 from the fill).
+ATTN_DRAM_TRAFFIC_BYTES_PER_UNIT = 248_423_936 / 64
 
 # Warp instructions per state update of the selective-scan kernel (8 states per thread), from a profiler count of
 # smsp__inst_executed.sum over one launch of the full configuration: 382.9 M instructions for 8 * 4096 * 4096 * 16
