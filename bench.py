@@ -61,7 +61,7 @@ REF_SHAPE = dict(B=1, H=32, S=4096, D=128)                  # the reference's ow
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 # DRAM bytes per launch of the attention kernel, per (batch, head) unit: a profiler capture of 64 units of the
-# full-size workload read and wrote 250.8 MB (dram__bytes_read.sum + dram__bytes_write.sum); the traffic grows in
+# full-size workload read and wrote 248.4 MB (dram__bytes_read.sum + dram__bytes_write.sum); the traffic grows in
 # proportion to the unit count because K/V of a head stay in L2 while its tiles run.  The compulsory traffic is
 # 4 * S * D * 2 bytes per unit = 4.19 MB; the capture is 7.4 % below it (part of Q/K/V was still in L2 from the fill).
 ATTN_DRAM_TRAFFIC_BYTES_PER_UNIT = 248_423_936 / 64
