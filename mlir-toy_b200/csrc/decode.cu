@@ -284,7 +284,9 @@ constexpr int kRingSmem = kRingStages * 2 * kStageBytes + 128;         // stages
 struct RingBarriers {
   uint64_t full[kRingStages], empty[kRingStages];
   int abort_flag;
+  int stage_rows[kRingStages];   // dynamic deal only: rows in the stage, 0 = no more stages
 };
+constexpr int kChunkRows = 4 * kStageRows;   // dynamic deal: rows a CTA takes from its head's counter at a time
 
 // Codes the ring kernel records in status[0] (block, detail and thread follow in status[1..3]).
 enum : int { kErrDecodeWait = 21, kErrDecodeBadPage = 22 };
@@ -317,7 +319,7 @@ __device__ __forceinline__ void bulk_load(uint32_t smem_dst, const void *gsrc, u
 // sequence on one GPU.  The ticket counters ([Hkv + 1] ints, zeroed once by the caller) are reset by the last CTA.
 struct DecodeTail {
   float *local;            // [Hq][D + 2] fp32 scratch: this GPU's partial
-  int *counters;           // [Hkv + 1], zero between launches
+  int *counters;           // [Hkv + 1] tickets, then [Hkv] chunk counters; zero between launches
   peer::Ptrs peers;        // symmetric buffers of all ranks (unused when world == 1)
   void *out;               // [Hq][D] in out_dtype (or [Hq][D + 2] fp32)
   int world, rank, out_dtype;
@@ -434,10 +436,16 @@ __device__ __forceinline__ void decode_tail(const DecodeTail &t, const float *pa
       else peer::combine_row<NB200_F32>(gathered, slot, t.world, row, t.out, lane);
     }
   }
-  if (tid <= Hkv) t.counters[tid] = 0;             // ready for the next launch (also after an expired wait)
+  for (int i = tid; i <= 2 * Hkv; i += blockDim.x) t.counters[i] = 0;   // ready for the next launch (also after an expired wait)
 }
 
-template <int DT, int G, bool TAIL = false>
+// DYN (one sequence, dense cache, with the fused tail): a 1-D grid of n_splits * Hkv CTAs, CTA l working for kv head
+// (l % Hkv + l / Hkv) % Hkv.  Instead of a fixed range of rows a CTA takes chunks of kChunkRows rows from its head's counter (the
+// first one is its own index, so nothing waits at the start).  Two CTAs share an SM and the one launched first gets
+// the larger share of it: with fixed ranges the first 148 CTAs of a one-wave launch finished at 152 us and the
+// other 148 at 178 us (measured), the GPU half idle in between.  Interleaving the heads over the launch order gives
+// every head both kinds of CTA, and the counters let the faster ones take more chunks.
+template <int DT, int G, bool TAIL = false, bool DYN = false>
 __global__ void __launch_bounds__(kRingThreads, (G >= 8 ? 1 : 2))
 decode_splitk_ring_kernel(const uint16_t *__restrict__ q, const uint16_t *__restrict__ k,
                           const uint16_t *__restrict__ v, float *__restrict__ partials, int Hkv, int Lkv,
@@ -450,7 +458,11 @@ decode_splitk_ring_kernel(const uint16_t *__restrict__ q, const uint16_t *__rest
   const uint32_t ring_base = sm100::smem_u32(ring);
   const uint32_t b_full = sm100::smem_u32(&bars->full[0]), b_empty = sm100::smem_u32(&bars->empty[0]);
 
-  const int split = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
+  const int split = DYN ? static_cast<int>(blockIdx.x) / Hkv : static_cast<int>(blockIdx.x);
+  // DYN: row `split` of the launch order is a rotation of the heads, so that a head's CTAs fall on even and odd SMs and
+  // on both resident slots alike (the odd SM of a pair, like the second CTA of an SM, gets the smaller share)
+  const int hkv = DYN ? (static_cast<int>(blockIdx.x) % Hkv + split) % Hkv : static_cast<int>(blockIdx.y);
+  const int b = DYN ? 0 : static_cast<int>(blockIdx.z);
   const int Hq = Hkv * G;
   // Dense cache: split s covers rows [floor(s*L/n), floor((s+1)*L/n)) of a [B, Hkv, L, D] tensor.
   // Paged cache (block_table != nullptr): a sequence of seq_lens[b] rows lives in pages of 64 rows, page p of it
@@ -501,7 +513,56 @@ decode_splitk_ring_kernel(const uint16_t *__restrict__ q, const uint16_t *__rest
 
   if (warp == kDecodeWarps) {
     // ================================ producer ================================
-    if (lane == 0) {
+    if (lane == 0 && DYN) {
+      const size_t head_base = ((size_t)b * Hkv + hkv) * Lkv * kHeadDim;
+      const int n_chunks = (Lkv + kChunkRows - 1) / kChunkRows;
+      int *counter = tail.counters + Hkv + 1 + hkv;
+      int it = 0;
+      bool gave_up = false;
+      int chunk = split;
+      while (chunk < n_chunks && !gave_up) {
+        const int next = n_splits + atomicAdd(counter, 1);   // asked for now, needed when this chunk's copies are out
+        const int row0 = chunk * kChunkRows;
+        const int rows_c = min(kChunkRows, Lkv - row0);
+        for (int r = 0; r < rows_c; r += kStageRows, ++it) {
+          const int st = it % kRingStages;
+          if (it >= kRingStages && !sm100::mbar_wait(b_empty + 8 * st, ((it / kRingStages) & 1) ^ 1, abort_flag)) {
+            decode_report(status, kErrDecodeWait, it);
+            gave_up = true;
+            break;
+          }
+          const int rows = min(kStageRows, rows_c - r);
+          const uint32_t bytes = static_cast<uint32_t>(rows) * kHeadDim * 2;
+          bars->stage_rows[st] = rows;
+          sm100::mbar_arrive_expect_tx(b_full + 8 * st, 2 * bytes);
+          const size_t off = head_base + (size_t)(row0 + r) * kHeadDim;
+          bulk_load(ring_base + st * 2 * kStageBytes, k + off, bytes, b_full + 8 * st);
+          bulk_load(ring_base + st * 2 * kStageBytes + kStageBytes, v + off, bytes, b_full + 8 * st);
+        }
+        chunk = next;
+      }
+      if (!gave_up) {   // the end marker: a stage of no rows
+        const int st = it % kRingStages;
+        if (it >= kRingStages && !sm100::mbar_wait(b_empty + 8 * st, ((it / kRingStages) & 1) ^ 1, abort_flag)) {
+          decode_report(status, kErrDecodeWait, it);
+          gave_up = true;
+        } else {
+          bars->stage_rows[st] = 0;
+          sm100::mbar_arrive(b_full + 8 * st);
+        }
+      }
+      if (gave_up) {  // let the copies in flight land before the CTA's shared memory goes away
+        for (int spin = 0; spin < 100000; ++spin) {
+          bool done = true;
+          for (int n = 0; n < kRingStages; ++n) {
+            const int j = it - 1 - n;
+            if (j >= 0) done = done && sm100::mbar_try_wait(b_full + 8 * (j % kRingStages), (j / kRingStages) & 1);
+          }
+          if (done) break;
+          __nanosleep(100);
+        }
+      }
+    } else if (lane == 0) {
       const size_t kv_base = (((size_t)b * Hkv + hkv) * Lkv + (size_t)t0) * kHeadDim;
       int issued = 0;
       for (int it = 0; it < n_iter; ++it) {
@@ -556,7 +617,7 @@ decode_splitk_ring_kernel(const uint16_t *__restrict__ q, const uint16_t *__rest
       }
     }
     const bool b3 = lane & 8, b2 = lane & 4;
-    for (int it = 0; it < n_iter; ++it) {
+    for (int it = 0; DYN || it < n_iter; ++it) {
       const int st = it % kRingStages;
       ok = __all_sync(0xffffffffu, sm100::mbar_wait(b_full + 8 * st, (it / kRingStages) & 1, abort_flag));
       if (!ok) {
@@ -565,14 +626,18 @@ decode_splitk_ring_kernel(const uint16_t *__restrict__ q, const uint16_t *__rest
       }
       const unsigned char *sk = ring + st * 2 * kStageBytes + (warp * (kPairs * 2) + half) * (kHeadDim * 2) + c * 16;
       const unsigned char *sv = sk + kStageBytes;
-      const int r0 = it * kStageRows + warp * (kPairs * 2) + half;
+      const int srows = DYN ? *reinterpret_cast<volatile int *>(&bars->stage_rows[st]) : 0;
+      if (DYN && srows == 0) break;   // the end marker
+      // row of this lane's first pair and the limit it is compared with: inside the stage, or inside the split
+      const int r0 = (DYN ? 0 : it * kStageRows) + warp * (kPairs * 2) + half;
+      const int r_end = DYN ? srows : T;
 
       // ---- scores: partial dot products over this lane's 8 elements ----
       bool valid[kPairs];
       float part[kPairs][G];
 #pragma unroll
       for (int i = 0; i < kPairs; ++i) {
-        valid[i] = r0 + 2 * i < T;
+        valid[i] = r0 + 2 * i < r_end;
         uint4 kr = *reinterpret_cast<const uint4 *>(sk + i * (2 * kHeadDim * 2));
         if (!valid[i]) kr = make_uint4(0, 0, 0, 0);   // rows past the end of the split were not copied
         const uint32_t ws[4] = {kr.x, kr.y, kr.z, kr.w};
@@ -928,7 +993,7 @@ extern "C" int nb200_decode_splitk(const void *q, const void *k, const void *v, 
 
 namespace {
 
-size_t sharded_local_offset(int Hkv) { return ((size_t)(Hkv + 1) * sizeof(int) + 255) / 256 * 256; }
+size_t sharded_local_offset(int Hkv) { return ((size_t)(2 * Hkv + 1) * sizeof(int) + 255) / 256 * 256; }
 size_t sharded_partials_offset(int Hq, int Hkv) {
   return sharded_local_offset(Hkv) + ((size_t)Hq * (kHeadDim + 2) * sizeof(float) + 255) / 256 * 256;
 }
@@ -936,10 +1001,10 @@ size_t sharded_partials_offset(int Hq, int Hkv) {
 template <int DT, int GV>
 int launch_sharded(const void *q, const void *k, const void *v, float *partials, int Hkv, int Lkv, int n_splits,
                    float scale_log2, int *status, const DecodeTail &tail, cudaStream_t st) {
-  NB200_CHECK_CUDA(cudaFuncSetAttribute(decode_splitk_ring_kernel<DT, GV, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingSmem));
-  NB200_CHECK_CUDA(cudaFuncSetAttribute(decode_splitk_ring_kernel<DT, GV, true>, cudaFuncAttributePreferredSharedMemoryCarveout,
+  NB200_CHECK_CUDA(cudaFuncSetAttribute(decode_splitk_ring_kernel<DT, GV, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingSmem));
+  NB200_CHECK_CUDA(cudaFuncSetAttribute(decode_splitk_ring_kernel<DT, GV, true, true>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                         cudaSharedmemCarveoutMaxShared));
-  decode_splitk_ring_kernel<DT, GV, true><<<dim3(n_splits, Hkv, 1), dim3(kRingThreads), kRingSmem, st>>>(
+  decode_splitk_ring_kernel<DT, GV, true, true><<<dim3(n_splits * Hkv), dim3(kRingThreads), kRingSmem, st>>>(
       static_cast<const uint16_t *>(q), static_cast<const uint16_t *>(k), static_cast<const uint16_t *>(v), partials, Hkv, Lkv,
       n_splits, scale_log2, nullptr, nullptr, 0, 0, status, tail);
   NB200_CHECK_CUDA(cudaGetLastError());

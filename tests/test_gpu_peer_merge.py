@@ -130,7 +130,7 @@ def test_one_launch_decode_of_a_whole_sequence(cuda, native_lib, Hq, Hkv, L, S):
         torch.cuda.synchronize()
         assert lib.nb200_status_read(status.data_ptr(), None, None) == 0
         assert (out.float().cpu() - ref).abs().max().item() <= 2e-2
-    assert int(ws[:4 * (Hkv + 1)].view(torch.int32).abs().sum()) == 0      # tickets are back at zero
+    assert int(ws[:4 * (2 * Hkv + 1)].view(torch.int32).abs().sum()) == 0  # tickets and chunk counters are back at zero
 
 
 def test_one_launch_sharded_decode_with_the_other_rank_played_by_the_host(cuda, native_lib):
