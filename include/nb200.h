@@ -197,7 +197,7 @@ int nb200_decode_merge_peer(const float *local_partial, void *const *peer_buffer
  *   peer_buffers, generation, wait_ns, status : as for nb200_decode_merge_peer (buffers sized with rows = Hq);
  *                  with world == 1 they are not used and the call is a one-launch decode of one sequence
  * n_splits * Hkv CTAs are launched; choose n_splits so that they fill the GPU's resident slots (two per SM) once.
- * The rows of a kv head are not cut into n_splits fixed ranges: its CTAs take chunks of 256 rows from a counter in
+ * The rows of a kv head are not cut into n_splits fixed ranges: its CTAs take chunks of 128 rows from a counter in
  * the workspace, so CTAs that get a smaller share of their SM do fewer chunks and all end together.
  */
 size_t nb200_decode_sharded_workspace_bytes(int Hq, int Hkv, int D, int n_splits);
