@@ -408,6 +408,10 @@ ssd_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
 #pragma unroll
       for (int k = 0; k < kP; ++k) acc[k] = 0.f;
       if (seg > 0) {
+        // The kernel is launched as a programmatic dependent of the segment-state kernel: it may start before that
+        // one has ended (first segments, which need nothing from it, run on the SMs it leaves idle); the states are
+        // read only behind this wait, which returns once the whole segment-state grid has finished.
+        asm volatile("griddepcontrol.wait;" ::: "memory");
         const size_t slot0 = (static_cast<size_t>(b) * H + h) * (nseg - 1);
         float lg = 0.f;
         for (int j = seg - 1; j >= 0; --j) {
@@ -624,6 +628,7 @@ ssd_segment_state_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
     if (threadIdx.x == 0) ssd_report(status, kErrSsdAlign, static_cast<int>(base));
     return;
   }
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the fused kernel may be scheduled from now on
   SegBarriers *bars = reinterpret_cast<SegBarriers *>(smem + kSegStages * kSegStageBytes);
   volatile int *abort_flag = &bars->abort_flag;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -868,8 +873,19 @@ int launch_ssd(const void *x, const float *dt, const float *A, const void *Bm, c
     NB200_CHECK_CUDA(cudaGetLastError());
   }
   NB200_CHECK_CUDA(cudaFuncSetAttribute(ssd_fused_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSsdSmem));
-  ssd_fused_kernel<DT><<<dim3(B * (H / plan.lanes) * plan.nseg), dim3(kSsdThreads), kSsdSmem, st>>>(
-      tx, tb, tc, ty, tdt, dt_by_tma, dt, A, L, H, G, plan.lanes, plan.nseg, plan.steps_per_seg, seg_states, seg_totals, status);
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(B * (H / plan.lanes) * plan.nseg);
+  cfg.blockDim = dim3(kSsdThreads);
+  cfg.dynamicSmemBytes = kSsdSmem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr{};
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = plan.nseg > 1 ? 1 : 0;   // behind the segment-state kernel only
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  NB200_CHECK_CUDA(cudaLaunchKernelEx(&cfg, ssd_fused_kernel<DT>, tx, tb, tc, ty, tdt, dt_by_tma, dt, A, L, H, G, plan.lanes,
+                                      plan.nseg, plan.steps_per_seg, static_cast<const float *>(seg_states),
+                                      static_cast<const float *>(seg_totals), status));
   NB200_CHECK_CUDA(cudaGetLastError());
   return NB200_OK;
 }
